@@ -67,7 +67,8 @@ PYBIND11_MODULE(_aien_host, m) {
     py::enum_<GroupKind>(m, "GroupKind")
         .value("Full", GroupKind::Full)
         .value("Window", GroupKind::Window)
-        .value("State", GroupKind::State);
+        .value("State", GroupKind::State)
+        .value("Chunk", GroupKind::Chunk);
 
     py::class_<GroupSpec>(m, "GroupSpec")
         .def(py::init([](GroupKind kind, int window, int capacity) {

@@ -21,6 +21,7 @@ CacheManager::CacheManager(int page_size, std::vector<GroupSpec> groups, int max
         const GroupSpec& s = groups_[g];
         if (s.capacity < 0) throw std::invalid_argument("group capacity must not be negative");
         if (s.kind == GroupKind::Window && s.window <= 0) throw std::invalid_argument("window must be positive");
+        if (s.kind == GroupKind::Chunk && s.window <= 0) throw std::invalid_argument("chunk size must be positive");
         refs_[g].assign(s.capacity, 0);
         free_[g].reserve(s.capacity);
         for (int p = s.capacity - 1; p >= 0; --p) free_[g].push_back(p);   // page 0 is handed out first
@@ -70,6 +71,7 @@ void CacheManager::drop_page(int g, int page) {
 }
 
 int CacheManager::first_needed_page(int g, int next_pos) const {
+    if (groups_[g].kind == GroupKind::Chunk) return (next_pos / groups_[g].window) * groups_[g].window / page_size_;
     if (groups_[g].kind != GroupKind::Window) return 0;
     const int first_key = next_pos - groups_[g].window + 1;
     return first_key <= 0 ? 0 : first_key / page_size_;

@@ -4,6 +4,8 @@
 // of which request, for every *group* of layers with the same needs:
 //   Full    every key is kept until the request ends;
 //   Window  only the last `window` keys are needed, pages the window has passed are given back;
+//   Chunk   a token sees only the keys of its own chunk of `window` positions (chunks counted from
+//           position 0): pages that lie wholly before the chunk of the next token are given back;
 //   State   one slot of fixed size per request (no pages).
 // Each paged group has its own pool and each request one block table per group.
 //
@@ -22,11 +24,11 @@
 
 namespace aien {
 
-enum class GroupKind : int { Full = 0, Window = 1, State = 2 };
+enum class GroupKind : int { Full = 0, Window = 1, State = 2, Chunk = 3 };
 
 struct GroupSpec {
     GroupKind kind = GroupKind::Full;
-    int window = 0;      // Window groups: keys visible to a token, itself included
+    int window = 0;      // Window groups: keys visible to a token, itself included; Chunk groups: positions per chunk
     int capacity = 0;    // pages (paged groups) or slots (State groups)
 };
 

@@ -92,6 +92,8 @@ int Scheduler::total_pages_for(int g, int tokens, int portion) const {
     const GroupSpec& spec = cache_->group(g);
     int full = ceil_div(tokens, ps);
     if (spec.kind == GroupKind::Window) full = std::min(full, ceil_div(spec.window + portion, ps) + 1);
+    // a chunk group holds at most the chunk a portion starts in plus the portion itself
+    if (spec.kind == GroupKind::Chunk) full = std::min(full, ceil_div(spec.window + portion, ps) + 1);
     return full;
 }
 

@@ -1,5 +1,8 @@
 // Paged causal grouped-query attention, one block per (query token, query head), any head size
-// up to 256, any number of heads and groups, any page size, optional window.
+// up to 256, any number of heads and groups, any page size, optional window, optional chunk
+// mask (a token sees only keys of its own chunk of `chunk` positions, counted from position 0),
+// optional per-head sink (one more term exp(sink[h]) in the softmax denominator, with no key and
+// no value), values of their own size `hdv` <= head size.
 //
 // It serves the true-32-bit engine for every kind of step (whole prompts, portions with an
 // offset, single decoded tokens) and is the plain kernel the faster attention kernels are
@@ -23,7 +26,8 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
                                const int* __restrict__ block_table, int max_blocks,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                TO* __restrict__ out, long out_stride,
-                               int nq, int nkv, int hd, int page_size, int window, float scale) {
+                               int nq, int nkv, int hd, int page_size, int window, float scale,
+                               int chunk, const float* __restrict__ sinks, int hdv) {
     __shared__ float qs[256];
     __shared__ float p[AG_THREADS];
     __shared__ int slots[AG_THREADS];
@@ -32,7 +36,8 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
     const int pos = positions[t];
     const int* bt = block_table + (size_t)seq_of_token[t] * max_blocks;
     const int kvh = h / (nq / nkv);
-    const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0 && (pos / chunk) * chunk > start) start = (pos / chunk) * chunk;
 
     for (int d = tid; d < hd; d += AG_THREADS) qs[d] = to_f(q[(size_t)t * q_stride + (size_t)h * hd + d]);
     __syncthreads();
@@ -69,17 +74,25 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
             const int sl = slots[jj];
             if (sl < 0) continue;
             const float pj = p[jj];
-            const TKV* vp = v_cache + ((size_t)sl * nkv + kvh) * hd;
-            if (tid < hd) acc0 = fmaf(pj, to_f(vp[tid]), acc0);
-            if (tid + AG_THREADS < hd) acc1 = fmaf(pj, to_f(vp[tid + AG_THREADS]), acc1);
+            const TKV* vp = v_cache + ((size_t)sl * nkv + kvh) * hdv;
+            if (tid < hdv) acc0 = fmaf(pj, to_f(vp[tid]), acc0);
+            if (tid + AG_THREADS < hdv) acc1 = fmaf(pj, to_f(vp[tid + AG_THREADS]), acc1);
         }
         m = m_new;
         __syncthreads();
     }
+    if (sinks != nullptr) {                            // the sink joins the denominator once, unscaled
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+        acc0 *= corr;
+        acc1 *= corr;
+    }
     const float inv = l > 0.f ? 1.0f / l : 0.f;        // empty context gives zeros (backend.rs:320)
-    TO* o = out + (size_t)t * out_stride + (size_t)h * hd;
-    if (tid < hd) o[tid] = from_f<TO>(acc0 * inv);
-    if (tid + AG_THREADS < hd) o[tid + AG_THREADS] = from_f<TO>(acc1 * inv);
+    TO* o = out + (size_t)t * out_stride + (size_t)h * hdv;
+    if (tid < hdv) o[tid] = from_f<TO>(acc0 * inv);
+    if (tid + AG_THREADS < hdv) o[tid + AG_THREADS] = from_f<TO>(acc1 * inv);
 }
 
 }  // namespace aien
@@ -90,14 +103,15 @@ AIEN_API int aien_paged_attention_generic(
     const void* q, long q_stride, const void* k_cache, const void* v_cache,
     const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
     void* out, long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale,
-    int act_dt, int kv_dt, int T, cudaStream_t stream) {
+    int act_dt, int kv_dt, int T, int chunk, const float* sinks, int hdv, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (hd <= 0 || hd > 256 || nkv <= 0 || nq % nkv != 0 || page_size <= 0) return AIEN_E_SHAPE;
+    if (hdv <= 0) hdv = hd;
+    if (hd <= 0 || hd > 256 || hdv > 256 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || chunk < 0) return AIEN_E_SHAPE;
     if (T > 65535) return AIEN_E_SHAPE;
     dim3 grid(nq, T);
     AIEN_DISPATCH_DTYPE(act_dt, TQ, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
         (paged_attention_generic_kernel<TQ, TKV, TQ><<<grid, AG_THREADS, 0, stream>>>(
             (const TQ*)q, q_stride, (const TKV*)k_cache, (const TKV*)v_cache, block_table, max_blocks,
-            seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale))));
+            seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale, chunk, sinks, hdv))));
     return launch_status();
 }

@@ -1,0 +1,107 @@
+// The norm of a residual branch's *output*, added into the stream:
+//
+//     x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w        y[t] = sum_p a[p][t] + sum_p b[p][t]
+//
+// for blocks that norm what a sublayer returns instead of what it reads.  The branch output may
+// come as one tensor or as float32 partial products (a product cut over K, or the weighted
+// outputs of routed experts, one part per choice) and as two such sources (routed parts plus a
+// shared expert); parts are added in index order, `a` before `b`.  The sum of squares, the scale
+// and the sum into x are float32.  `h` (optional) receives the updated row in the compute dtype:
+// the next sublayer reads x itself, so the copy it multiplies by is made here and not by a pass
+// of its own.  One CTA per row; the weight vector is the effective one (an offset already added).
+#include "common.cuh"
+
+namespace aien {
+
+template <typename T>
+__device__ __forceinline__ float parts_sum(const T* __restrict__ p, int nparts, size_t part_stride, size_t idx) {
+    float d = 0.f;
+    for (int i = 0; i < nparts; ++i) d += ld_act(p + (size_t)i * part_stride + idx);
+    return d;
+}
+
+constexpr int BN_THREADS = 256;
+constexpr int BN_KEEP = 8;        // values of the row a thread keeps in registers between the passes
+
+template <typename TA, typename TB, typename TH>
+__global__ void __launch_bounds__(BN_THREADS)
+branch_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_parts, size_t a_stride,
+                       const TB* __restrict__ b, int b_parts, size_t b_stride,
+                       const void* __restrict__ w, int wdt, float eps, TH* __restrict__ h, int H) {
+    __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float keep[BN_KEEP];
+    float ss = 0.f;
+    int n = 0;
+    for (int i = threadIdx.x; i < H; i += BN_THREADS, ++n) {
+        float v = parts_sum(a, a_parts, a_stride, base + i);
+        if (b != nullptr) v += parts_sum(b, b_parts, b_stride, base + i);
+        if (n < BN_KEEP) keep[n] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)H + eps);
+    n = 0;
+    for (int i = threadIdx.x; i < H; i += BN_THREADS, ++n) {
+        float v;
+        if (n < BN_KEEP) {
+            v = keep[n];
+        } else {                                           // rows wider than 2,048: summed again, same order, same bits
+            v = parts_sum(a, a_parts, a_stride, base + i);
+            if (b != nullptr) v += parts_sum(b, b_parts, b_stride, base + i);
+        }
+        const float r = x[base + i] + v * scale * load_dyn(w, wdt, i);
+        x[base + i] = r;
+        if (h != nullptr) h[base + i] = from_f<TH>(r);
+    }
+}
+
+// x[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w in place (the norm of the embedding row), h as above.
+template <typename TH>
+__global__ void __launch_bounds__(BN_THREADS)
+stream_norm_inplace_kernel(float* __restrict__ x, const void* __restrict__ w, int wdt, float eps, TH* __restrict__ h, int H) {
+    __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += BN_THREADS) {
+        const float v = __ldcg(x + base + i);
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += BN_THREADS) {
+        const float r = __ldcg(x + base + i) * scale * load_dyn(w, wdt, i);
+        x[base + i] = r;
+        if (h != nullptr) h[base + i] = from_f<TH>(r);
+    }
+}
+
+}  // namespace aien
+
+using namespace aien;
+
+// a_dt / b_dt: dtype of the sources (float32 when they have several parts); h_dt: dtype of h.
+AIEN_API int aien_branch_norm_add(float* x, const void* a, int a_dt, int a_parts, size_t a_stride,
+                                  const void* b, int b_dt, int b_parts, size_t b_stride,
+                                  const void* w, int w_dt, float eps, void* h, int h_dt, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || a == nullptr || a_parts < 1 || (b != nullptr && b_parts < 1)) return AIEN_E_SHAPE;
+    if ((a_parts > 1 && a_dt != AIEN_DT_F32) || (b != nullptr && b_parts > 1 && b_dt != AIEN_DT_F32)) return AIEN_E_DTYPE;
+    AIEN_DISPATCH_DTYPE(a_dt, TA, AIEN_DISPATCH_DTYPE(b_dt, TB, AIEN_DISPATCH_DTYPE(h_dt, TH,
+        (launch_chain(branch_norm_add_kernel<TA, TB, TH>, dim3(T), dim3(BN_THREADS), 0, stream,
+                      x, (const TA*)a, a_parts, a_stride, (const TB*)b, b_parts, b_stride, w, w_dt, eps, (TH*)h, H)))));
+    return launch_status();
+}
+
+AIEN_API int aien_stream_norm_inplace(float* x, const void* w, int w_dt, float eps, void* h, int h_dt, int T, int H,
+                                      cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0) return AIEN_E_SHAPE;
+    AIEN_DISPATCH_DTYPE(h_dt, TH,
+        (launch_chain(stream_norm_inplace_kernel<TH>, dim3(T), dim3(BN_THREADS), 0, stream, x, w, w_dt, eps, (TH*)h, H)));
+    return launch_status();
+}

@@ -85,7 +85,8 @@ class Engine:
         # "state" [runs, slots + 1, *shape], the extra slot being nobody's (padding rows use it).
         # Zero-filled: kernels that load whole pages need finite values everywhere.
         gspecs, self.storage = [], []
-        kinds = {"full": self.host.GroupKind.Full, "window": self.host.GroupKind.Window, "state": self.host.GroupKind.State}
+        kinds = {"full": self.host.GroupKind.Full, "window": self.host.GroupKind.Window, "state": self.host.GroupKind.State,
+                 "chunk": self.host.GroupKind.Chunk}
         for need, slots in zip(model.group_needs, model.group_slots):
             if need.kind == "state":
                 gspecs.append(self.host.GroupSpec(kinds["state"], 0, self.max_requests))

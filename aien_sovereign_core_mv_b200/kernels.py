@@ -117,7 +117,14 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
         "aien_convert": [P, I, P, I, c_size_t, P],
         "aien_gemm_simple": [P, I, L, P, I, L, P, I, L, I, I, I, P],
-        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, P],
+        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P],
+        "aien_branch_norm_add": [P, P, I, I, c_size_t, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
+        "aien_stream_norm_inplace": [P, P, I, F, P, I, I, I, P],
+        "aien_qk_rope_pairs_unit_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, I, I, F, P, P, I, P, P, P, I, I, I, P],
+        "aien_moe_route": [P, I, I, I, I, I, I, P, P, P],
+        "aien_moe_expert_up": [P, I, L, P, I, P, P, I, I, I, I, I, I, P],
+        "aien_moe_expert_down": [P, I, P, I, P, P, P, I, I, I, I, P],
+        "aien_act_rows": [P, I, c_size_t, I, P],
         "aien_argmax_rows": [P, I, I, P, P],
         "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
         "aien_sample_rows_logprob": [P, I, I, P, P, P, P, P, P, P, P, P, P],
@@ -344,6 +351,133 @@ def qk_norm_rope_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optiona
         dt(q_out), dt(k_cache) if k_cache is not None else dt(q_out), T, _stream()), "qk_norm_rope_kv_write")
 
 
+def _source(t: Optional[torch.Tensor], shape) -> tuple:
+    """(pointer, dtype code, parts, part stride) of a branch output: [T,H], or float32 parts [P,T,H]."""
+    if t is None:
+        return 0, F32, 1, 0
+    n, stride = _parts_of(t, shape)
+    return _p(t), dt(t), n, stride
+
+
+def branch_norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, b: Optional[torch.Tensor] = None,
+                    h: Optional[torch.Tensor] = None) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * weight with y = a (+ b): the norm of a branch's output, added
+    into the float32 stream.  a and b are [T,H] tensors or float32 parts [P,T,H] (added in order).
+    ``h`` (optional, [T,H]) receives the updated rows in its own dtype."""
+    _dev(x, a, b, weight, h)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.numel() == H and weight.is_contiguous()
+    if h is not None:
+        assert h.is_contiguous() and tuple(h.shape) == (T, H)
+    pa, da, na, sa = _source(a, x.shape)
+    pb, db, nb, sb = _source(b, x.shape)
+    _check(lib().aien_branch_norm_add(_p(x), pa, da, na, sa, pb, db, nb, sb, _p(weight), dt(weight), float(eps),
+                                      _p(h), dt(h) if h is not None else F32, T, H, _stream()), "branch_norm_add")
+
+
+def stream_norm_inplace(x: torch.Tensor, weight: torch.Tensor, eps: float, h: Optional[torch.Tensor] = None) -> None:
+    """x = x / sqrt(mean(x^2) + eps) * weight in place (float32 rows); ``h`` as in branch_norm_add."""
+    _dev(x, weight, h)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.numel() == H and weight.is_contiguous()
+    if h is not None:
+        assert h.is_contiguous() and tuple(h.shape) == (T, H)
+    _check(lib().aien_stream_norm_inplace(_p(x), _p(weight), dt(weight), float(eps), _p(h), dt(h) if h is not None else F32,
+                                          T, H, _stream()), "stream_norm_inplace")
+
+
+def qk_rope_pairs_unit_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], head_dim: int,
+                                value_dim: int, unit: bool, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                                rotary_dim: int, slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                                v_cache: Optional[torch.Tensor], q_out: torch.Tensor) -> None:
+    """Rotation over neighbouring pairs (2i, 2i+1) of the first ``rotary_dim`` values of every q and
+    k head, then (``unit``) division by the head's root mean square; q to ``q_out``, k to its cache
+    slot, and as values the first ``value_dim`` values of the k head as projected (``v`` None) or of
+    the v head.  q [T, nq*hd], k [T, nkv*hd] may be column slices of one product's output, or of
+    float32 partial products [P, T, ...]."""
+    _dev(q, k, v, cos, sin, slot_map, k_cache, v_cache, q_out)
+    nparts, part_stride = 1, 0
+    if q.dim() == 3:
+        assert q.dtype == torch.float32
+        nparts, part_stride = q.shape[0], q.stride(0)
+        assert k is None or (k.dim() == 3 and k.stride(0) == part_stride)
+        assert v is None or (v.dim() == 3 and v.stride(0) == part_stride)
+    T = q.shape[-2]
+    assert q.stride(-1) == 1 and q.shape[-1] % head_dim == 0 and q_out.stride(1) == 1 and q_out.shape == (T, q.shape[-1])
+    nq, nkv = q.shape[-1] // head_dim, 0
+    if k is not None:
+        assert slot_map is not None and k_cache is not None and v_cache is not None and k.stride(-1) == 1 and k.dtype == q.dtype
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype
+        assert slot_map.dtype == torch.int32 and slot_map.numel() >= T
+        nkv = k.shape[-1] // head_dim
+        assert v is None or (v.stride(-1) == 1 and v.dtype == q.dtype and v.shape[-1] == nkv * value_dim)
+    if cos is not None:
+        assert sin is not None and cos.shape == (T, rotary_dim // 2) and cos.is_contiguous() and sin.is_contiguous()
+    _check(lib().aien_qk_rope_pairs_unit_kv_write(
+        _p(q), q.stride(-2), nq, _p(k), k.stride(-2) if k is not None else 0, _p(v), v.stride(-2) if v is not None else 0, nkv,
+        dt(q), nparts, part_stride, _p(q_out), q_out.stride(0), head_dim, int(value_dim), 1 if unit else 0, float(eps),
+        _p(cos), _p(sin), rotary_dim if cos is not None else 0, _p(slot_map), _p(k_cache), _p(v_cache),
+        dt(q_out), dt(k_cache) if k_cache is not None else dt(q_out), T, _stream()), "qk_rope_pairs_unit_kv_write")
+
+
+# ---------------------------------------------------------------------------- routed feed-forward
+ACT_KINDS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1}
+
+
+def moe_route(z: torch.Tensor, groups: int, keep: int, top: int, renorm: bool, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """From router logits z [T,E] (float32): softmax scores, the ``keep`` best of ``groups`` equal groups of
+    neighbouring experts (a group scores its best expert), the ``top`` best experts of those; ids int32
+    [T,top], wts float32 [T,top] = their scores (``renorm``: divided by their sum)."""
+    _dev(z, ids, wts)
+    T, E = z.shape
+    assert z.dtype == torch.float32 and z.is_contiguous() and ids.dtype == torch.int32 and wts.dtype == torch.float32
+    assert ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top and wts.numel() >= T * top
+    _check(lib().aien_moe_route(_p(z), T, E, int(groups), int(keep), int(top), 1 if renorm else 0, _p(ids), _p(wts), _stream()),
+           "moe_route")
+
+
+def moe_expert_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor, top: int, act_kind: int) -> None:
+    """act[t*top + c] = f(w_up[ids[t,c]] . h[t]); h [T,D], w_up [E,F,D], act [T*top, F]."""
+    _dev(h, w_up, ids, act)
+    T, D = h.shape
+    E, Fd, D2 = w_up.shape
+    assert D2 == D and h.stride(1) == 1 and w_up.is_contiguous() and act.is_contiguous() and tuple(act.shape) == (T * top, Fd)
+    _check(lib().aien_moe_expert_up(_p(h), dt(h), h.stride(0), _p(w_up), dt(w_up), _p(ids), _p(act), dt(act), T, int(top), D, Fd,
+                                    int(act_kind), _stream()), "moe_expert_up")
+
+
+def moe_expert_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, parts: torch.Tensor, top: int) -> None:
+    """parts[c, t] = wts[t,c] * (w_down[ids[t,c]] . act[t*top + c]); w_down [E,D,F], parts float32 [top,T,D]."""
+    _dev(act, w_down, ids, wts, parts)
+    E, D, Fd = w_down.shape
+    T = act.shape[0] // top
+    assert act.is_contiguous() and act.shape[1] == Fd and w_down.is_contiguous()
+    assert parts.dtype == torch.float32 and parts.is_contiguous() and tuple(parts.shape) == (top, T, D)
+    _check(lib().aien_moe_expert_down(_p(act), dt(act), _p(w_down), dt(w_down), _p(ids), _p(wts), _p(parts), T, int(top), D, Fd,
+                                      _stream()), "moe_expert_down")
+
+
+def moe_workspace_bytes(lim, num_experts: int, top: int, hidden: int, expert_ff: int) -> int:
+    """Scratch of the grouped expert products for the largest step."""
+    return 4096
+
+
+def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
+                parts: torch.Tensor, top: int, act_kind: int) -> None:
+    """parts[c, t] = wts[t,c] * w_down[e] f(w_up[e] h[t]) with e = ids[t,c]: the chosen experts of every token."""
+    T = h.shape[0]
+    act = ctx.workspace.take((T * top, w_up.shape[1]), ctx.dtype)
+    moe_expert_up(h, w_up, ids, act, top, act_kind)
+    moe_expert_down(act, w_down, ids, wts, parts, top)
+
+
+def act_rows(a: torch.Tensor, act_kind: int) -> None:
+    """a = f(a) in place: 0 the erf gelu, 1 the tanh gelu."""
+    _dev(a)
+    assert a.is_contiguous()
+    _check(lib().aien_act_rows(_p(a), dt(a), a.numel(), int(act_kind), _stream()), "act_rows")
+
+
 def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
     _dev(src, dst)
     assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
@@ -366,10 +500,15 @@ def gemm_simple(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                             max_blocks: int, seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                             num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                            scale: float) -> None:
+                            scale: float, chunk: int = 0, sinks: Optional[torch.Tensor] = None, value_dim: int = 0) -> None:
     """Causal attention of T query tokens over their requests' pages.  q [T, nq*hd] (row stride
-    free), caches [slots, nkv, hd], block_table int32 [S, max_blocks], out [T, nq*hd]."""
-    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out)
+    free), caches [slots, nkv, hd], block_table int32 [S, max_blocks], out [T, nq*hd].
+    ``chunk`` > 0: a token sees only the keys of its own chunk of that many positions.  ``sinks``
+    (float32 [nq]): one more term exp(sink) in every head's softmax denominator.  ``value_dim``:
+    size of a value when it differs from the head size (v_cache [slots, nkv, value_dim], out [T, nq*value_dim])."""
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, sinks)
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
     assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype
@@ -377,7 +516,7 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     _check(lib().aien_paged_attention_generic(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
         _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window, float(scale),
-        dt(q), dt(k_cache), T, _stream()), "paged_attention_generic")
+        dt(q), dt(k_cache), T, int(chunk), _p(sinks), int(value_dim), _stream()), "paged_attention_generic")
 
 
 # ---------------------------------------------------------------------------- sampling
@@ -766,6 +905,24 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
+
+
+def chunk_attention_workspace_bytes(lim, num_heads: int, value_dim: int, key_span: int) -> int:
+    """Scratch of attention under a chunk mask for the largest step: a token sees at most ``key_span`` keys."""
+    return 4096
+
+
+def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor,
+                         num_q_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, window: int, chunk: int,
+                         sinks: Optional[torch.Tensor], scale: float) -> None:
+    """Attention of the step's tokens over one cache group under a chunk mask (``chunk`` > 0: a token
+    sees the keys of its own chunk of that many positions), an optional window, and an optional
+    per-head softmax sink; values of size ``value_dim``.  Picks the kernel for the step."""
+    k2 = k_cache.view(-1, num_kv_heads, head_dim)
+    v2 = v_cache.view(-1, num_kv_heads, value_dim)
+    paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                            chunk=chunk, sinks=sinks, value_dim=value_dim)
 
 
 def prefill_attention_supports(q: torch.Tensor, k_cache: torch.Tensor, out: torch.Tensor, head_dim: int) -> bool:

@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import Prenormed, Block, CacheNeed, Mixer, RunBinding, StepContext
+from ..parts.base import Prenormed, Block, CacheNeed, Mixer, RunBinding, StepContext, StreamCopy
 from ..registry import make_part, part_factory
 
 
@@ -193,7 +193,7 @@ class Decoder:
             else:
                 delta = block.forward(ctx, x, delta, binding)
         ws.end_layers()
-        if isinstance(delta, Prenormed):          # the last block has no next norm; a block of another kind may still return one
+        if isinstance(delta, (Prenormed, StreamCopy)):    # nothing is pending: the last block summed into the stream itself
             delta = None
         if num_rows > 0:
             rows = ws.take((num_rows, self.hidden_size), torch.float32)

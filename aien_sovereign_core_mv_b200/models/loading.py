@@ -14,6 +14,8 @@ from .decoder import Decoder
 def model_spec_for(raw_config: Mapping, generation_config: Optional[Mapping] = None, strict: bool = False):
     """(typed config, ModelSpec) for a parsed config.json, through the architecture registry."""
     archs = raw_config.get("architectures") if isinstance(raw_config, Mapping) else None
+    if archs is None and isinstance(raw_config, Mapping) and isinstance(raw_config.get("architecture"), str):
+        archs = [raw_config["architecture"]]           # configurations that name their one architecture as a string
     if not isinstance(archs, (list, tuple)) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"config.json: architectures must name exactly one architecture, got {archs!r}")
     try:

@@ -29,6 +29,8 @@ class PagedAttention(Mixer):
             raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         if head_dim % 2 or head_dim > 256:
             raise ValueError(f"head_dim {head_dim}: the attention kernels take even sizes up to 256")
+        if getattr(position, "pairing", "halves") != "halves":
+            raise ValueError("this mixer rotates halves (i with i + d/2); interleaved pairs belong to 'chunked_sink_attention'")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.position = position
         self.qk_norm, self.qk_norm_eps = bool(qk_norm), float(qk_norm_eps)

@@ -37,8 +37,9 @@ class CacheNeed:
     """What a mixer keeps between steps.
 
     kind "full" (every token's entry stays), "window" (only the last ``window`` tokens' entries
-    are needed; pages behind them are given back) or "state" (one tensor of fixed size per
-    request).  A paged kind names its **planes**: what is stored per token, as (name, shape)
+    are needed; pages behind them are given back), "chunk" (a token needs only the entries of its
+    own chunk of ``window`` positions, chunks counted from position 0; pages before the chunk of
+    the next token are given back) or "state" (one tensor of fixed size per request).  A paged kind names its **planes**: what is stored per token, as (name, shape)
     pairs, e.g. keys and values of grouped-query attention ``(("k", (nkv, hd)), ("v", (nkv,
     hd)))`` or one latent ``(("latent", (r,)),)``.  The engine allocates, for every plane,
     ``[runs of the group, tokens of the pool, *shape]`` in the compute dtype (or ``dtype``) and
@@ -207,6 +208,16 @@ class Prenormed:
 
 
 @dataclass
+class StreamCopy:
+    """What a block that sums its branches into the stream itself hands on instead of a pending
+    sum: nothing is pending, and ``h`` is the residual stream as it stands, in the compute dtype
+    (made by the kernel that wrote the last sum).  A block whose sublayers read the stream itself
+    takes ``h`` as their input; every other consumer treats it as "nothing pending"."""
+
+    h: torch.Tensor
+
+
+@dataclass
 class ResidualSink:
     """Offered to a part whose last product ends a residual branch: instead of returning the
     branch's output for the next norm to add, the product may add it to ``x`` itself and return a
@@ -238,6 +249,13 @@ class Part:
 
 class Norm(Part):
     def forward(self, ctx: StepContext, x: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_normed(self, ctx: StepContext, x: torch.Tensor, a, b=None, want_copy: bool = False):
+        """x += norm(a + b): the norm of a branch's *output* (a tensor, or float32 parts [P,T,H];
+        ``b`` a second such source), summed into the float32 stream.  With ``want_copy`` returns
+        the updated stream in the compute dtype (x itself for a float32 engine).  For blocks that
+        norm what a sublayer returns rather than what it reads."""
         raise NotImplementedError
 
     def sink(self, ctx: StepContext, x: torch.Tensor) -> Optional[ResidualSink]:
@@ -307,7 +325,7 @@ def add_to_residual(ctx: StepContext, x: torch.Tensor, delta) -> None:
     partial products [P, T, H], or a Prenormed (whose sum is in x already).  For blocks that do
     not fuse the residual sum into a norm."""
     from .. import kernels as K
-    if delta is None or isinstance(delta, Prenormed):
+    if delta is None or isinstance(delta, (Prenormed, StreamCopy)):
         return
     K.add_residual(x, delta)
 

@@ -6,7 +6,7 @@ from typing import Optional
 import torch
 
 from .. import kernels as K
-from ..registry import register_embedding, register_head
+from ..registry import make_part, register_embedding, register_head
 from .base import Embedding, Head, StepContext
 from .linear import linear
 
@@ -32,6 +32,35 @@ class TableEmbedding(Embedding):
 
     def forward(self, ctx: StepContext, token_ids: torch.Tensor, x: torch.Tensor) -> None:
         K.embed_gather(self.weight, token_ids, x)
+
+
+@register_embedding("table_normed")
+class NormedTableEmbedding(TableEmbedding):
+    """x[t] = norm(weight[token_ids[t]]): a table whose rows pass a norm before they become the
+    residual stream.  ``norm`` names a registered norm part ({"kind": ..., further parameters});
+    its tensors are this part's ``norm.<local name>``.  A head tied to this embedding multiplies
+    by the table itself."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, norm: dict):
+        super().__init__(vocab_size, hidden_size)
+        params = {k: v for k, v in dict(norm).items() if k != "kind"}
+        self.norm = make_part("norm", norm["kind"], size=self.hidden_size, **params)
+        if not hasattr(self.norm, "norm_stream"):
+            raise ValueError(f"norm kind {norm['kind']!r} cannot norm the stream in place")
+
+    def param_shapes(self):
+        shapes = dict(super().param_shapes())
+        for local, spec in self.norm.param_shapes().items():
+            shapes[f"norm.{local}"] = spec
+        return shapes
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.norm.bind({k[len("norm."):]: v for k, v in tensors.items() if k.startswith("norm.")})
+
+    def forward(self, ctx: StepContext, token_ids: torch.Tensor, x: torch.Tensor) -> None:
+        K.embed_gather(self.weight, token_ids, x)
+        self.norm.norm_stream(ctx, x)
 
 
 @register_head("linear")

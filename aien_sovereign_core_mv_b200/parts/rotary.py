@@ -11,11 +11,13 @@ from ..registry import register_position
 from .base import Position, StepContext
 
 
-def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None):
+def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None,
+                        theta_as_float32: bool = True):
     """inv_freq_i = theta^(-2i/d) in float64 (theta itself held as float32, as the reference
-    does), optionally smoothed the llama3 way (crates/aien-abi-core/src/lib.rs:69-84, 106-114)."""
+    does, unless ``theta_as_float32`` is off), optionally smoothed the llama3 way
+    (crates/aien-abi-core/src/lib.rs:69-84, 106-114)."""
     d = rotary_dim or head_dim
-    theta32 = float(torch.tensor(theta, dtype=torch.float32).item())
+    theta32 = float(torch.tensor(theta, dtype=torch.float32).item()) if theta_as_float32 else float(theta)
     inv = [1.0 / theta32 ** ((2 * i) / d) for i in range(d // 2)]
     if scaling:
         old = float(scaling["original_max_position_embeddings"])
@@ -37,18 +39,24 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict] = N
 
 @register_position("rotary")
 class RotaryPosition(Position):
-    """rotate_half pairing (i, i + d/2); angle = position * inv_freq in float64, cos and sin
-    rounded to float32 (crates/aien-inference-abi/src/tensor.rs:150-188).  The table of a step
-    is built once and shared by every layer that uses the same part."""
+    """angle = position * inv_freq in float64, cos and sin rounded to float32
+    (crates/aien-inference-abi/src/tensor.rs:150-188).  The table of a step is built once and
+    shared by every layer that uses the same part.  ``pairing`` says which dimensions a mixer
+    rotates together: "halves" (i with i + d/2, rotate_half) or "interleaved" (2i with 2i+1); the
+    table is the same, the mixer's kernel reads ``pairing``."""
 
-    def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None):
+    def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None,
+                 pairing: str = "halves", theta_as_float32: bool = True):
+        if pairing not in ("halves", "interleaved"):
+            raise ValueError(f"rotary pairing {pairing!r}: 'halves' or 'interleaved'")
+        self.pairing = pairing
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim or head_dim)
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.theta = float(theta)
         self.scaling = dict(scaling) if scaling else None
-        self._inv_host = inverse_frequencies(self.head_dim, self.theta, self.scaling, self.rotary_dim)
+        self._inv_host = inverse_frequencies(self.head_dim, self.theta, self.scaling, self.rotary_dim, bool(theta_as_float32))
         self._inv_dev: Optional[torch.Tensor] = None
 
     def step_workspace_bytes(self, max_tokens):

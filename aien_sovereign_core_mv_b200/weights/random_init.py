@@ -27,11 +27,16 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 def random_tensor(name: str, shape: Tuple[int, ...], kind: str, seed: int,
                   init_std: Optional[float] = None, device: str = "cpu") -> torch.Tensor:
-    """``kind``: "matrix" ([out, in]), "embedding", or "norm" (a vector of scales)."""
+    """``kind``: "matrix" ([out, in]), "embedding", "norm" (a vector of scales around one), "norm_offset"
+    (a vector of scales stored around zero) or "vector" (free numbers of order one, e.g. softmax sinks)."""
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
     if kind == "norm":
         t = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 0.4 + 0.8
+    elif kind == "norm_offset":
+        t = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 0.4 - 0.2
+    elif kind == "vector":
+        t = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
     elif kind == "embedding":
         t = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
         t *= 1.0 if init_std is None else init_std
