@@ -128,7 +128,8 @@ def run_trace(model_dir, dtype, out_dir, max_tokens, steps, page_size=None, time
         if proc.poll() is None:
             proc.kill()
     with open(os.path.join(model_dir, "config.json")) as f:
-        vocab = json.load(f)["vocab_size"]
+        cfg = json.load(f)
+        vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     out = {}
     for s in steps:
         path = os.path.join(out_dir, f"{s['step']}.f32")
