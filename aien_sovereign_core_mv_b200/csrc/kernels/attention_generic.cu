@@ -2,7 +2,8 @@
 // up to 256, any number of heads and groups, any page size, optional window, optional chunk
 // mask (a token sees only keys of its own chunk of `chunk` positions, counted from position 0),
 // optional per-head sink (one more term exp(sink[h]) in the softmax denominator, with no key and
-// no value), values of their own size `hdv` <= head size.
+// no value), values of their own size `hdv` <= head size, optionally only the tokens that
+// `token_list` names (T of them).
 //
 // It serves the true-32-bit engine for every kind of step (whole prompts, portions with an
 // offset, single decoded tokens) and is the plain kernel the faster attention kernels are
@@ -27,12 +28,12 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                TO* __restrict__ out, long out_stride,
                                int nq, int nkv, int hd, int page_size, int window, float scale,
-                               int chunk, const float* __restrict__ sinks, int hdv) {
+                               int chunk, const float* __restrict__ sinks, int hdv, const int* __restrict__ token_list) {
     __shared__ float qs[256];
     __shared__ float p[AG_THREADS];
     __shared__ int slots[AG_THREADS];
     __shared__ float red[32];
-    const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
+    const int h = blockIdx.x, t = token_list ? token_list[blockIdx.y] : blockIdx.y, tid = threadIdx.x;
     const int pos = positions[t];
     const int* bt = block_table + (size_t)seq_of_token[t] * max_blocks;
     const int kvh = h / (nq / nkv);
@@ -103,7 +104,7 @@ AIEN_API int aien_paged_attention_generic(
     const void* q, long q_stride, const void* k_cache, const void* v_cache,
     const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
     void* out, long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale,
-    int act_dt, int kv_dt, int T, int chunk, const float* sinks, int hdv, cudaStream_t stream) {
+    int act_dt, int kv_dt, int T, int chunk, const float* sinks, int hdv, const int* token_list, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hdv <= 0) hdv = hd;
     if (hd <= 0 || hd > 256 || hdv > 256 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || chunk < 0) return AIEN_E_SHAPE;
@@ -112,6 +113,6 @@ AIEN_API int aien_paged_attention_generic(
     AIEN_DISPATCH_DTYPE(act_dt, TQ, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
         (paged_attention_generic_kernel<TQ, TKV, TQ><<<grid, AG_THREADS, 0, stream>>>(
             (const TQ*)q, q_stride, (const TKV*)k_cache, (const TKV*)v_cache, block_table, max_blocks,
-            seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale, chunk, sinks, hdv))));
+            seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale, chunk, sinks, hdv, token_list))));
     return launch_status();
 }

@@ -1,5 +1,8 @@
 // Prefill attention over the paged bfloat16 cache: portions of prompts (any length, any offset
-// into their request) beside single tokens, causal, grouped-query, optional window.
+// into their request) beside single tokens, causal, grouped-query, optional window, optional
+// chunk mask (a query sees only the keys of its own chunk of `chunk` positions, counted from
+// position 0; key blocks that lie wholly before the chunk of a warp's first row are skipped),
+// optional per-head sink (one more term exp(sink[h]) in the softmax denominator).
 //
 // One CTA of eight warps handles 128 consecutive query tokens of one request for one query head;
 // the host lists these tiles (request, offset into its portion).  Keys are visited in blocks of
@@ -51,7 +54,8 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
                                const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                                const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
                                __nv_bfloat16* __restrict__ out, long out_stride,
-                               int nq, int nkv, int page_size, int window, float scale_log2e) {
+                               int nq, int nkv, int page_size, int window, float scale_log2e,
+                               int chunk, const float* __restrict__ sinks) {
     constexpr int STR = HD + 8;                   // row stride in elements: an odd number of 16-byte chunks
     constexpr int KS = HD / 16;                   // k16 steps of the score product
     constexpr int DT = HD / 8;                    // n8 tiles of the output
@@ -70,7 +74,8 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
     const int rows = min(AP_BM, q_len - q0);
     const int pos0 = ctx_len[s] - q_len + q0;                      // position of the tile's first query
     const int pos_last = pos0 + rows - 1;
-    const int first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    int first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    if (chunk > 0) first = max(first, (pos0 / chunk) * chunk);         // later rows of the tile start no earlier
     const int kvh = h / (nq / nkv);
     const int* bt = block_table + (size_t)s * max_blocks;
 
@@ -120,7 +125,13 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
     for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int qpos0 = pos0 + warp * 16 + g, qpos1 = qpos0 + 8;       // positions of this thread's two rows
-    const int wlo0 = window > 0 ? qpos0 - window + 1 : 0, wlo1 = window > 0 ? qpos1 - window + 1 : 0;
+    int wlo0 = window > 0 ? qpos0 - window + 1 : 0, wlo1 = window > 0 ? qpos1 - window + 1 : 0;
+    int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;       // the lowest key any row of this warp sees
+    if (chunk > 0) {
+        wlo0 = max(wlo0, (qpos0 / chunk) * chunk);
+        wlo1 = max(wlo1, (qpos1 / chunk) * chunk);
+        warp_lo = max(warp_lo, ((pos0 + warp * 16) / chunk) * chunk);
+    }
 
     for (int kb = kb_begin; kb <= kb_end; ++kb) {
         const bool more = kb < kb_end;
@@ -128,7 +139,7 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
         if (more) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads();                             // K(kb), V(kb) have landed for every thread
         const uint32_t Ks_u = KV_u + (uint32_t)((kb - kb_begin) & 1) * BUF_BYTES, Vs_u = Ks_u + V_OFF;
-        if (active && kb * AP_BN <= pos0 + warp * 16 + 15) {     // the block is not wholly in this warp's future
+        if (active && kb * AP_BN <= pos0 + warp * 16 + 15 && (kb + 1) * AP_BN > warp_lo) {     // the block is neither wholly in this warp's future nor wholly before what it sees
         float sc[AP_BN / 8][4];
 #pragma unroll
         for (int j = 0; j < AP_BN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
@@ -205,6 +216,17 @@ paged_prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_strid
 
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1); l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+    if (sinks != nullptr) {                          // the sink joins each row's denominator once (log2 units like the scores)
+        const float sk = sinks[h] * 1.4426950408889634f;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const float mn = fmaxf(m_run[r], sk);
+            const float corr = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - mn);
+            l_run[r] = l_run[r] * corr + exp2f(sk - mn);
+#pragma unroll
+            for (int d = 0; d < DT; ++d) { o[d][2 * r] *= corr; o[d][2 * r + 1] *= corr; }
+        }
+    }
     const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
     const int r0 = warp * 16 + g, r1 = r0 + 8;
 #pragma unroll
@@ -221,7 +243,7 @@ template <int HD>
 static int launch_prefill(const void* q, long q_stride, const void* kc, const void* vc, const int* bt, int max_blocks,
                           const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
                           void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale,
-                          cudaStream_t stream) {
+                          int chunk, const float* sinks, cudaStream_t stream) {
     constexpr int STR = HD + 8;
     const int smem = (AP_BM + 4 * AP_BN) * STR * 2;
     auto kern = paged_prefill_attention_kernel<HD>;
@@ -233,7 +255,7 @@ static int launch_prefill(const void* q, long q_stride, const void* kc, const vo
     dim3 grid(num_tiles, nq);
     kern<<<grid, AP_THREADS, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
                                               bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, (__nv_bfloat16*)out, out_stride,
-                                              nq, nkv, page_size, window, scale * 1.4426950408889634f);
+                                              nq, nkv, page_size, window, scale * 1.4426950408889634f, chunk, sinks);
     return launch_status();
 }
 
@@ -246,8 +268,10 @@ using namespace aien;
 AIEN_API int aien_paged_attention_prefill(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
-    void* out, long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+    void* out, long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, int chunk, const float* sinks,
+    cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
+    if (chunk < 0) return AIEN_E_SHAPE;
     if (hd <= 0 || hd > 128 || (hd & 15) || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || nq > 65535) return AIEN_E_SHAPE;
     if ((q_stride & 7) || (out_stride & 1) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
         ((uintptr_t)out & 3))
@@ -255,7 +279,7 @@ AIEN_API int aien_paged_attention_prefill(
 #define AP_CASE(HDV)                                                                                                   \
     if (hd == HDV)                                                                                                     \
         return launch_prefill<HDV>(q, q_stride, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, tile_seq,  \
-                                   tile_q0, num_tiles, out, out_stride, nq, nkv, page_size, window, scale, stream);
+                                   tile_q0, num_tiles, out, out_stride, nq, nkv, page_size, window, scale, chunk, sinks, stream);
     AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
 #undef AP_CASE
     return AIEN_E_SHAPE;

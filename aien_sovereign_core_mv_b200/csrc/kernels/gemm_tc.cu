@@ -204,6 +204,142 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// The grouped form, for routed experts: the rows of A are sorted by group (expert), every group's
+// run of rows starts at a multiple of 128, and W holds the groups' matrices one below the other
+// ([groups * N, K]).  Row tile i belongs to group tile_group[i] (-1: the tile is empty and its CTA
+// leaves at once) and is multiplied by rows group * N + n0 .. of W.  The roles, the ring and the
+// bounded waits are those of the first form with 128 rows of A.  tile_group comes from a kernel
+// ahead in the stream, so nothing is requested before griddepcontrol.wait here.
+//   EPI 0: store;  EPI 2 / 3: the gelu in its erf / tanh form, then store.
+//   row_dest != nullptr: row r of the result goes to row row_dest[r] of out (-1: nowhere) times
+//   row_scale[r]: the weighted outputs of routed experts, back in token order.
+// Columns of a tile beyond N belong to the next group's rows of W; they are computed and not stored.
+__device__ __forceinline__ float tc_gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
+__device__ __forceinline__ float tc_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+template <int EPI, typename TC>
+__global__ void __launch_bounds__(192)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                       TC* __restrict__ out, long ldc, const int* __restrict__ tile_group, const int* __restrict__ row_dest,
+                       const float* __restrict__ row_scale, int N, int K) {
+    constexpr int AR = 128, BN = 128;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    constexpr int TC_STAGES = TcT<AR, BN>::STAGES, TC_STAGE_A = TcT<AR, BN>::STAGE_A, TC_STAGE_B = TcT<AR, BN>::STAGE_B;
+    const uint32_t sA = base, sB = base + TC_STAGES * TC_STAGE_A;
+    const uint32_t bars = sB + TC_STAGES * TC_STAGE_B;
+    const uint32_t full0 = bars, empty0 = bars + 8 * TC_STAGES, tmem_full = bars + 16 * TC_STAGES;
+    const uint32_t tmem_slot = tmem_full + 8;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + (tmem_slot - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    griddep_launch();
+    griddep_wait();
+    const int group = __ldcg(tile_group + blockIdx.x);
+    if (group < 0) return;                               // the whole CTA: nothing was allocated yet
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+    const int w0 = group * N + n0;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TcT<AR, BN>::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % TC_STAGES;
+                const uint32_t round = kb / TC_STAGES;
+                if (round > 0) mbar_wait(empty0 + 8 * s, (round - 1) & 1, 1);
+                mbar_expect_tx(full0 + 8 * s, TC_STAGE_A + TC_STAGE_B);
+                tma_load_2d(sA + s * TC_STAGE_A, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                tma_load_2d(sB + s * TC_STAGE_B, &map_w, full0 + 8 * s, kb * TC_BK, w0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % TC_STAGES;
+                mbar_wait(full0 + 8 * s, (kb / TC_STAGES) & 1, 2);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = make_desc_sw128(sA + s * TC_STAGE_A), db = make_desc_sw128(sB + s * TC_STAGE_B);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        const int quarter = warp & 3;
+        mbar_wait(tmem_full, 0, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row = m0 + quarter * 32 + lane;
+        int dest = row;
+        float rs = 1.0f;
+        if (row_dest != nullptr) {
+            dest = __ldcg(row_dest + row);
+            rs = __ldcg(row_scale + row);
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN && n0 + c0 < N; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (EPI == 2) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(tc_gelu_erf(__uint_as_float(r[j])));
+            } else if (EPI == 3) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(tc_gelu_tanh(__uint_as_float(r[j])));
+            }
+            if (row_dest != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs);
+            }
+            if (dest >= 0) tc_store_chunk<0, TC>(r, out, ldc, dest, n0, c0, N);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TcT<AR, BN>::TMEM_COLS) : "memory");
+    }
+}
+
+template <int EPI, typename TC>
+static int launch_tc_grouped(const void* A, long lda, int rows_a, const void* W, long ldw, int groups, void* out, long ldc,
+                             const int* tile_group, int tiles, const int* row_dest, const float* row_scale, int N, int K,
+                             cudaStream_t stream) {
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, (uint64_t)rows_a, (uint64_t)K, (uint64_t)lda, TC_BK, 128u) ||
+        !make_map(&mw, W, (uint64_t)groups * (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BK, 128u))
+        return AIEN_E_STATE;
+    auto kern = gemm_tc_grouped_kernel<EPI, TC>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcT<128, 128>::SMEM) != cudaSuccess) return AIEN_E_STATE;
+        configured = true;
+    }
+    dim3 grid(tiles, (N + 127) / 128);
+    launch_chain(kern, grid, dim3(192), (size_t)TcT<128, 128>::SMEM, stream, ma, mw, (TC*)out, ldc, tile_group, row_dest, row_scale, N, K);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
 // The persistent form, for products whose tile grid fills the GPU: one CTA per SM walks over
 // tiles of 128 x BN (BN 256), M-tiles fastest.  Tensor memory holds two
 // accumulators, so the four epilogue warps drain tile i while the MMA lane already works on
@@ -714,6 +850,34 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
         if (c_dt == AIEN_DT_F32) return launch_tc<1, float>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
         return AIEN_E_DTYPE;
     }
+    return AIEN_E_SHAPE;
+}
+
+// Grouped product (see gemm_tc_grouped_kernel): A [tiles * 128, K] sorted by group, W [groups * N, K].
+// epilogue 0 store, 2 erf gelu, 3 tanh gelu.  row_dest / row_scale (both or neither): scatter rows of
+// the result, scaled, into out (float32).
+AIEN_API int aien_gemm_tc_grouped(const void* A, long lda, const void* W, long ldw, int groups, void* out, int c_dt, long ldc,
+                                  const int* tile_group, int tiles, const int* row_dest, const float* row_scale,
+                                  int N, int K, int epilogue, cudaStream_t stream) {
+    if (tiles <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || groups <= 0 || tile_group == nullptr) return AIEN_E_SHAPE;
+    if ((row_dest == nullptr) != (row_scale == nullptr)) return AIEN_E_SHAPE;
+    if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
+    if ((N + 127) / 128 > 65535 || (long)groups * N > 2147483647L) return AIEN_E_SHAPE;
+    const int rows_a = tiles * 128;
+#define TCG_CASE(EPIV, T) return launch_tc_grouped<EPIV, T>(A, lda, rows_a, W, ldw, groups, out, ldc, tile_group, tiles, row_dest, row_scale, N, K, stream)
+    if (c_dt == AIEN_DT_BF16) {
+        if (epilogue == 0) TCG_CASE(0, __nv_bfloat16);
+        if (epilogue == 2) TCG_CASE(2, __nv_bfloat16);
+        if (epilogue == 3) TCG_CASE(3, __nv_bfloat16);
+    } else if (c_dt == AIEN_DT_F32) {
+        if (epilogue == 0) TCG_CASE(0, float);
+        if (epilogue == 2) TCG_CASE(2, float);
+        if (epilogue == 3) TCG_CASE(3, float);
+    } else {
+        return AIEN_E_DTYPE;
+    }
+#undef TCG_CASE
     return AIEN_E_SHAPE;
 }
 

@@ -129,6 +129,138 @@ moe_expert_down_kernel(const TA* __restrict__ act, const TW* __restrict__ w_down
     if (lane == 0) parts[((size_t)c * T + t) * D + n] = acc * __ldcg(wts + pair);
 }
 
+// ---------------------------------------------------------------- rows sorted by expert, for the grouped product
+// One CTA.  Pair p = t * top + c chose expert ids[p].  Every expert's pairs get a run of rows that
+// starts at a multiple of 128 (the row tile of the grouped tensor-core product); the runs follow one
+// another in expert order.  Out: tile_group[i] = expert of row tile i (-1 beyond the last run);
+// row_pair[r] = the pair in row r (-1: padding); row_dest[r] = c * T + t, the row of the [top, T, D]
+// parts that the pair's output belongs to (-1: padding); row_scale[r] = the pair's weight.
+// Which row of its run a pair gets depends on the order the threads arrive in; no result depends on
+// it, since a row of a product depends on that row alone.
+constexpr int SORT_THREADS = 1024;
+
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_pairs_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int P, int T, int top, int E, int max_tiles,
+                      int* __restrict__ tile_group, int* __restrict__ row_pair, int* __restrict__ row_dest,
+                      float* __restrict__ row_scale) {
+    __shared__ int count[ROUTE_MAX_EXPERTS];
+    __shared__ int start[ROUTE_MAX_EXPERTS];      // first row of the expert's run; then the cursor into it
+    griddep_launch();
+    griddep_wait();
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += SORT_THREADS) count[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < P; p += SORT_THREADS) atomicAdd(&count[__ldcg(ids + p)], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int row = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = row;
+            row += (count[e] + 127) & ~127;
+        }
+        count[0] = row;                            // total rows in use, for the fill below
+    }
+    __syncthreads();
+    const int used_rows = count[0];
+    for (int i = tid; i < max_tiles; i += SORT_THREADS) tile_group[i] = -1;
+    for (int r = tid; r < max_tiles * 128; r += SORT_THREADS) { row_pair[r] = -1; row_dest[r] = -1; row_scale[r] = 0.f; }
+    __syncthreads();
+    for (int e = tid; e < E; e += SORT_THREADS) {
+        const int first = start[e] >> 7;
+        const int last = ((e + 1 < E ? start[e + 1] : used_rows) >> 7);
+        for (int i = first; i < last; ++i) tile_group[i] = e;
+    }
+    __syncthreads();
+    for (int p = tid; p < P; p += SORT_THREADS) {
+        const int e = __ldcg(ids + p);
+        const int r = atomicAdd(&start[e], 1);
+        const int t = p / top, c = p - t * top;
+        row_pair[r] = p;
+        row_dest[r] = c * T + t;
+        row_scale[r] = __ldcg(wts + p);
+    }
+}
+
+// a_sorted[r, :] = h[row_pair[r] / top, :] (zeros in padding rows); bfloat16, 16-byte vectors, D % 8 == 0.
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, long h_stride, const int* __restrict__ row_pair, int top,
+                       __nv_bfloat16* __restrict__ a_sorted, int D, int rows) {
+    griddep_launch();
+    griddep_wait();
+    const int vec = D >> 3;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)rows * vec; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / vec), v = (int)(i - (size_t)r * vec);
+        const int p = __ldcg(row_pair + r);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (p >= 0) val = __ldcg(reinterpret_cast<const uint4*>(h + (size_t)(p / top) * h_stride) + v);
+        reinterpret_cast<uint4*>(a_sorted + (size_t)r * D)[v] = val;
+    }
+}
+
+// ---------------------------------------------------------------- expert products of a few tokens (bfloat16)
+// A step that decodes brings few (token, choice) pairs, each with a whole expert's matrices to read:
+// the products are bound by that stream.  One warp per output value, 16-byte loads, ROWS output rows
+// of one pair per warp so that as many loads are in flight; K % 256 == 0 keeps every lane on whole vectors.
+__device__ __forceinline__ float dot8(const uint4 w, const uint4 a) {
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
+    const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 wf = __bfloat1622float2(wp[j]), af = __bfloat1622float2(ap[j]);
+        acc = fmaf(wf.x, af.x, acc);
+        acc = fmaf(wf.y, af.y, acc);
+    }
+    return acc;
+}
+
+constexpr int SV_ROWS = 4;        // output rows per warp
+
+// MODE 0: act[pair, f] = f(w[e, f, :] . x[pair / top, :])   (x = the tokens' rows, K = D)
+// MODE 1: parts[c, t, n] = wts[pair] * (w[e, n, :] . x[pair, :])  (x = the pairs' hidden rows, K = F)
+template <int MODE>
+__global__ void __launch_bounds__(256)
+moe_expert_rows_bf16_kernel(const __nv_bfloat16* __restrict__ x, long x_stride, const __nv_bfloat16* __restrict__ w,
+                            const int* __restrict__ ids, const float* __restrict__ wts, void* __restrict__ out,
+                            int T, int top, int N, int K, int act_kind) {
+    griddep_launch();
+    const int pair = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.y * 8 + (threadIdx.x >> 5)) * SV_ROWS;
+    griddep_wait();
+    if (n0 >= N) return;
+    const int e = __ldcg(ids + pair);
+    const int t = pair / top;
+    const __nv_bfloat16* xr = x + (size_t)(MODE == 0 ? t : pair) * x_stride;
+    const __nv_bfloat16* wr = w + ((size_t)e * N + n0) * K;
+    float acc[SV_ROWS];
+#pragma unroll
+    for (int j = 0; j < SV_ROWS; ++j) acc[j] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 a = __ldcg(reinterpret_cast<const uint4*>(xr + k));
+        uint4 wv[SV_ROWS];
+#pragma unroll
+        for (int j = 0; j < SV_ROWS; ++j)
+            wv[j] = (n0 + j < N) ? __ldg(reinterpret_cast<const uint4*>(wr + (size_t)j * K + k)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int j = 0; j < SV_ROWS; ++j) acc[j] += dot8(wv[j], a);
+    }
+#pragma unroll
+    for (int j = 0; j < SV_ROWS; ++j) acc[j] = warp_sum(acc[j]);
+    if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < SV_ROWS; ++j) {
+            if (n0 + j >= N) break;
+            if (MODE == 0) {
+                reinterpret_cast<__nv_bfloat16*>(out)[(size_t)pair * N + n0 + j] = __float2bfloat16_rn(act_apply(acc[j], act_kind));
+            } else {
+                const int c = pair - t * top;
+                reinterpret_cast<float*>(out)[((size_t)c * T + t) * N + n0 + j] = acc[j] * __ldcg(wts + pair);
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void act_rows_kernel(T* __restrict__ a, size_t n, int act_kind) {
     griddep_launch();
@@ -171,6 +303,46 @@ AIEN_API int aien_moe_expert_down(const void* act, int act_dt, const void* w_dow
     AIEN_DISPATCH_DTYPE(act_dt, TA, AIEN_DISPATCH_DTYPE(w_dt, TW,
         (launch_chain(moe_expert_down_kernel<TA, TW>, grid, dim3(256), 0, stream,
                       (const TA*)act, (const TW*)w_down, ids, wts, parts, T, top, D, F))));
+    return launch_status();
+}
+
+// Rows for the grouped product; the arrays hold max_tiles (tile_group) and max_tiles * 128 entries.
+AIEN_API int aien_moe_sort_pairs(const int* ids, const float* wts, int T, int top, int E, int max_tiles, int* tile_group,
+                                 int* row_pair, int* row_dest, float* row_scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const long P = (long)T * top;
+    if (E <= 0 || E > ROUTE_MAX_EXPERTS || top <= 0 || P > 2147483647L / 2 || (long)max_tiles * 128 < P + (long)E * 127) return AIEN_E_SHAPE;
+    launch_chain(moe_sort_pairs_kernel, dim3(1), dim3(SORT_THREADS), 0, stream, ids, wts, (int)P, T, top, E, max_tiles,
+                 tile_group, row_pair, row_dest, row_scale);
+    return launch_status();
+}
+
+AIEN_API int aien_moe_gather_rows(const void* h, long h_stride, const int* row_pair, int top, void* a_sorted, int D, int rows,
+                                  cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (D <= 0 || (D & 7) || (h_stride & 7) || ((uintptr_t)h & 15) || ((uintptr_t)a_sorted & 15)) return AIEN_E_ALIGN;
+    const size_t n = (size_t)rows * (D >> 3);
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    launch_chain(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)h, h_stride, row_pair, top,
+                 (__nv_bfloat16*)a_sorted, D, rows);
+    return launch_status();
+}
+
+// The expert products of a few tokens, bfloat16: mode 0 = up with activation (out bfloat16 [T*top, N], K = D),
+// mode 1 = down, weighted, into float32 parts [top, T, N] (K = F).  K % 256 == 0, 16-byte aligned rows.
+AIEN_API int aien_moe_expert_rows_bf16(int mode, const void* x, long x_stride, const void* w, const int* ids, const float* wts,
+                                       void* out, int T, int top, int N, int K, int act_kind, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (N <= 0 || K <= 0 || (K & 255) || (x_stride & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return AIEN_E_ALIGN;
+    const int tiles = (N + 8 * SV_ROWS - 1) / (8 * SV_ROWS);
+    if (tiles > 65535 || (long)T * top > 2147483647L) return AIEN_E_SHAPE;
+    dim3 grid(T * top, tiles);
+    if (mode == 0)
+        launch_chain(moe_expert_rows_bf16_kernel<0>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride,
+                     (const __nv_bfloat16*)w, ids, wts, out, T, top, N, K, act_kind);
+    else
+        launch_chain(moe_expert_rows_bf16_kernel<1>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride,
+                     (const __nv_bfloat16*)w, ids, wts, out, T, top, N, K, act_kind);
     return launch_status();
 }
 

@@ -117,7 +117,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
         "aien_convert": [P, I, P, I, c_size_t, P],
         "aien_gemm_simple": [P, I, L, P, I, L, P, I, L, I, I, I, P],
-        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P],
+        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P, P],
         "aien_branch_norm_add": [P, P, I, I, c_size_t, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
         "aien_stream_norm_inplace": [P, P, I, F, P, I, I, I, P],
         "aien_qk_rope_pairs_unit_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, I, I, F, P, P, I, P, P, P, I, I, I, P],
@@ -125,6 +125,10 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_moe_expert_up": [P, I, L, P, I, P, P, I, I, I, I, I, I, P],
         "aien_moe_expert_down": [P, I, P, I, P, P, P, I, I, I, I, P],
         "aien_act_rows": [P, I, c_size_t, I, P],
+        "aien_moe_sort_pairs": [P, P, I, I, I, I, P, P, P, P, P],
+        "aien_moe_gather_rows": [P, L, P, I, P, I, I, P],
+        "aien_moe_expert_rows_bf16": [I, P, L, P, P, P, P, I, I, I, I, I, P],
+        "aien_gemm_tc_grouped": [P, L, P, L, I, P, I, L, P, I, P, P, I, I, I, P],
         "aien_argmax_rows": [P, I, I, P, P],
         "aien_sample_rows": [P, I, I, P, P, P, P, P, P, P, P, P],
         "aien_sample_rows_logprob": [P, I, I, P, P, P, P, P, P, P, P, P, P],
@@ -143,7 +147,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_scale_rows_ssq": [P, L, P, I, F, P, L, I, I, P],
         "aien_gemm_tc_error": [],
         "aien_attention_prefill_tc_error": [],
-        "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
+        "aien_paged_attention_prefill": [P, L, P, P, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, I, P, P],
         "aien_paged_attention_prefill_tc": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_prefill_tc_split": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, P],
         "aien_paged_attention_prefill_tc_supports": [I, I],
@@ -457,16 +461,67 @@ def moe_expert_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, 
                                       _stream()), "moe_expert_down")
 
 
+MOE_ROWS_MAX_TOKENS = 16      # steps of up to this many tokens stream the chosen experts row by row
+
+
+def _moe_tiles(num_pairs: int, num_experts: int) -> int:
+    """Row tiles of 128 that the pairs sorted by expert can need: every expert's run is padded to whole tiles."""
+    return (num_pairs + 127) // 128 + num_experts
+
+
 def moe_workspace_bytes(lim, num_experts: int, top: int, hidden: int, expert_ff: int) -> int:
-    """Scratch of the grouped expert products for the largest step."""
-    return 4096
+    """Scratch of the grouped expert products for the largest step: the rows sorted by expert (inputs
+    and hidden activations, bfloat16) and their maps."""
+    tiles = _moe_tiles(lim.max_tokens * top, num_experts)
+    return tiles * 128 * ((hidden + expert_ff) * 2 + 12) + tiles * 4 + 8192
+
+
+_MOE_IMPL = __import__("os").environ.get("AIEN_B200_MOE", "").strip().lower()      # "plain" pins the plain kernels
+
+
+def moe_grouped_supports(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    D, Fd = w_up.shape[2], w_up.shape[1]
+    return (h.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16 and D % 8 == 0
+            and Fd % 8 == 0 and h.stride(1) == 1 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+            and w_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
 
 
 def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
                 parts: torch.Tensor, top: int, act_kind: int) -> None:
-    """parts[c, t] = wts[t,c] * w_down[e] f(w_up[e] h[t]) with e = ids[t,c]: the chosen experts of every token."""
-    T = h.shape[0]
-    act = ctx.workspace.take((T * top, w_up.shape[1]), ctx.dtype)
+    """parts[c, t] = wts[t,c] * w_down[e] f(w_up[e] h[t]) with e = ids[t,c]: the chosen experts of every token.
+    bfloat16: a few tokens stream their experts' rows (one warp per output value, 16-byte loads); larger
+    steps sort the (token, choice) pairs by expert and run two grouped tcgen05 products, the activation in
+    the first one's epilogue, the weights and the way back to token order in the second's.  float32, and
+    sizes those kernels do not take: the plain products."""
+    T, D = h.shape
+    E, Fd, _ = w_up.shape
+    ws = ctx.workspace
+    ok = _MOE_IMPL != "plain" and moe_grouped_supports(h, w_up, w_down)
+    if ok and T <= MOE_ROWS_MAX_TOKENS and D % 256 == 0 and Fd % 256 == 0:
+        act = ws.take((T * top, Fd), torch.bfloat16)
+        _check(lib().aien_moe_expert_rows_bf16(0, _p(h), h.stride(0), _p(w_up), _p(ids), _p(wts), _p(act), T, top, Fd, D,
+                                               int(act_kind), _stream()), "moe_expert_rows(up)")
+        _check(lib().aien_moe_expert_rows_bf16(1, _p(act), Fd, _p(w_down), _p(ids), _p(wts), _p(parts), T, top, D, Fd,
+                                               int(act_kind), _stream()), "moe_expert_rows(down)")
+        return
+    if ok and T > MOE_ROWS_MAX_TOKENS:
+        tiles = _moe_tiles(T * top, E)
+        rows = tiles * 128
+        tile_group = ws.take((tiles,), torch.int32)
+        row_pair = ws.take((rows,), torch.int32)
+        row_dest = ws.take((rows,), torch.int32)
+        row_scale = ws.take((rows,), torch.float32)
+        a_sorted = ws.take((rows, D), torch.bfloat16)
+        act = ws.take((rows, Fd), torch.bfloat16)
+        _check(lib().aien_moe_sort_pairs(_p(ids), _p(wts), T, top, E, tiles, _p(tile_group), _p(row_pair), _p(row_dest),
+                                         _p(row_scale), _stream()), "moe_sort_pairs")
+        _check(lib().aien_moe_gather_rows(_p(h), h.stride(0), _p(row_pair), top, _p(a_sorted), D, rows, _stream()), "moe_gather_rows")
+        _check(lib().aien_gemm_tc_grouped(_p(a_sorted), D, _p(w_up), D, E, _p(act), BF16, Fd, _p(tile_group), tiles, None, None,
+                                          Fd, D, 2 + int(act_kind), _stream()), "gemm_tc_grouped(up)")
+        _check(lib().aien_gemm_tc_grouped(_p(act), Fd, _p(w_down), Fd, E, _p(parts), F32, D, _p(tile_group), tiles, _p(row_dest),
+                                          _p(row_scale), D, Fd, 0, _stream()), "gemm_tc_grouped(down)")
+        return
+    act = ws.take((T * top, Fd), ctx.dtype)
     moe_expert_up(h, w_up, ids, act, top, act_kind)
     moe_expert_down(act, w_down, ids, wts, parts, top)
 
@@ -500,23 +555,26 @@ def gemm_simple(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                             max_blocks: int, seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                             num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                            scale: float, chunk: int = 0, sinks: Optional[torch.Tensor] = None, value_dim: int = 0) -> None:
+                            scale: float, chunk: int = 0, sinks: Optional[torch.Tensor] = None, value_dim: int = 0,
+                            token_list: Optional[torch.Tensor] = None, num_tokens: Optional[int] = None) -> None:
     """Causal attention of T query tokens over their requests' pages.  q [T, nq*hd] (row stride
     free), caches [slots, nkv, hd], block_table int32 [S, max_blocks], out [T, nq*hd].
     ``chunk`` > 0: a token sees only the keys of its own chunk of that many positions.  ``sinks``
     (float32 [nq]): one more term exp(sink) in every head's softmax denominator.  ``value_dim``:
-    size of a value when it differs from the head size (v_cache [slots, nkv, value_dim], out [T, nq*value_dim])."""
-    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, sinks)
+    size of a value when it differs from the head size (v_cache [slots, nkv, value_dim], out [T, nq*value_dim]).
+    ``token_list`` (int32) with ``num_tokens``: only these tokens of the step are served."""
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, sinks, token_list)
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads
-    T = q.shape[0]
+    T = q.shape[0] if token_list is None else int(num_tokens)
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
     assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype
     assert block_table.dtype == torch.int32 and seq_of_token.dtype == torch.int32 and positions.dtype == torch.int32
+    assert token_list is None or (token_list.dtype == torch.int32 and token_list.numel() >= T)
     _check(lib().aien_paged_attention_generic(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
         _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window, float(scale),
-        dt(q), dt(k_cache), T, int(chunk), _p(sinks), int(value_dim), _stream()), "paged_attention_generic")
+        dt(q), dt(k_cache), T, int(chunk), _p(sinks), int(value_dim), _p(token_list), _stream()), "paged_attention_generic")
 
 
 # ---------------------------------------------------------------------------- sampling
@@ -920,6 +978,21 @@ def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
     per-head softmax sink; values of size ``value_dim``.  Picks the kernel for the step."""
     k2 = k_cache.view(-1, num_kv_heads, head_dim)
     v2 = v_cache.view(-1, num_kv_heads, value_dim)
+    if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and value_dim == head_dim
+            and prefill_attention_supports(q, k2, out, head_dim)):
+        # portions go through the tiled tensor-core kernel, which skips the key blocks outside a warp's chunk;
+        # the single tokens beside them through the plain kernel
+        tile_seq, tile_q0, n = ctx.prefill_tiles
+        if n > 0:
+            paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
+                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, impl="mma",
+                                    chunk=chunk, sinks=sinks)
+        tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
+        if nd > 0:
+            paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                                    num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                                    chunk=chunk, sinks=sinks, value_dim=value_dim, token_list=tokens, num_tokens=nd)
+        return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
                             chunk=chunk, sinks=sinks, value_dim=value_dim)
@@ -952,15 +1025,21 @@ def prefill_split_scratch_bytes(num_tiles: int, num_q_heads: int, head_dim: int,
 
 def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                             out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale, impl: Optional[str] = None,
-                            scratch: Optional[torch.Tensor] = None, max_ctx: int = 0, splits: int = 0) -> None:
+                            scratch: Optional[torch.Tensor] = None, max_ctx: int = 0, splits: int = 0, chunk: int = 0,
+                            sinks: Optional[torch.Tensor] = None) -> None:
     """Causal attention of portions of prompts over their requests' pages (bfloat16, tensor
     cores).  ``tile_seq``/``tile_q0``: for every 128-token query tile, the index of its request in
     the step and the tile's offset inside that request's portion.  ``impl``: "tc" (tcgen05, where
     the sizes allow) or "mma" (mma.sync); default from ``AIEN_B200_PREFILL``, else "tc".
     ``scratch`` (float32, optional) with ``max_ctx`` (an upper bound of the contexts) lets the
     tcgen05 kernel cut the keys of a step with few tiles into ranges that run on separate SMs;
-    ``splits`` > 0 asks for that many ranges (tests)."""
-    _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out)
+    ``splits`` > 0 asks for that many ranges (tests).  ``chunk`` > 0 (a query sees only the keys of
+    its own chunk of that many positions) and ``sinks`` (float32 [heads], one more term exp(sink) in
+    the softmax denominator) are the mma.sync kernel's."""
+    _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out, sinks)
+    if chunk or sinks is not None:
+        impl = "mma"
+        assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     for t in (block_table, q_start, ctx_len, tile_seq, tile_q0):
@@ -979,7 +1058,7 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
     _check(lib().aien_paged_attention_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(q_start), _p(ctx_len), _p(tile_seq),
         _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window,
-        float(scale), _stream()), "paged_attention_prefill")
+        float(scale), int(chunk), _p(sinks), _stream()), "paged_attention_prefill")
 
 
 def attention_prefill_tc_error() -> int:

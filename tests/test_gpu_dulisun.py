@@ -223,6 +223,43 @@ def test_attention_sees_its_chunk_and_the_sink(dtype, chunk, page, hd, hdv, nq, 
     assert float((out2.float() - out.float()).abs().max()) > 0.05
 
 
+@pytest.mark.parametrize("chunk,page,hd,nq,nkv,offset,qlen", [(24, 16, 32, 4, 2, 0, 150), (64, 16, 64, 6, 1, 37, 300), (128, 32, 128, 2, 1, 200, 129),
+                                                              (100, 16, 48, 3, 3, 99, 2), (16, 16, 64, 2, 2, 15, 131)])
+def test_tiled_prefill_attention_sees_its_chunk_and_the_sink(chunk, page, hd, nq, nkv, offset, qlen):
+    """A portion of ``qlen`` queries that starts at position ``offset`` of its request, through the
+    tensor-core kernel: the keys at every chunk's two edges stand out, so a warp that skips a block
+    it needs, or a row that sees across its chunk's edge, shows."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(chunk * 3 + hd)
+    n = offset + qlen
+    keys = torch.randn(n, nkv, hd, generator=g)
+    vals = torch.randn(n, nkv, hd, generator=g)
+    for p in range(0, n, chunk):
+        keys[p] *= 3.0
+        if p > 0:
+            keys[p - 1] *= 3.0
+    qpos = list(range(offset, n))
+    q = torch.randn(qlen, nq, hd, generator=g).to(torch.bfloat16)
+    keys, vals = keys.to(torch.bfloat16), vals.to(torch.bfloat16)
+    sinks = torch.tensor([(-1.0) ** h * (0.5 + 1.5 * h) for h in range(nq)])
+    scale = 0.5 / math.sqrt(hd)
+    order = list(reversed(range((n + page - 1) // page + 1)))
+    kc, vc, row = _paged(keys, vals, page, order)
+    mb = len(row) + 2
+    bt = torch.full((2, mb), -1, dtype=torch.int32)
+    bt[1, :len(row)] = torch.tensor(row, dtype=torch.int32)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    tiles = list(range(0, qlen, 128))
+    out = torch.zeros(3 + qlen, nq * hd, dtype=torch.bfloat16).cuda()          # three tokens of another request come first
+    qfull = torch.zeros(3 + qlen, nq * hd, dtype=torch.bfloat16)
+    qfull[3:] = q.reshape(qlen, -1)
+    K.paged_attention_prefill(qfull.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), mb, i32([0, 3, 3 + qlen]), i32([3, n]), i32([1] * len(tiles)),
+                              i32(tiles), len(tiles), out, nq, nkv, hd, page, 0, scale, chunk=chunk, sinks=sinks.cuda())
+    want = pd.chunk_sink_attention(q.double().numpy(), keys.double().numpy(), vals.double().numpy(), qpos, list(range(n)), scale, chunk,
+                                   sinks.double().numpy())
+    H.assert_close(out[3:].float().cpu().numpy().reshape(qlen, nq, hd), want, 2e-2, "tiled attention")
+
+
 @pytest.mark.parametrize("E,count,keep,top", [(8, 4, 2, 3), (12, 2, 1, 2), (4, 1, 1, 1), (6, 6, 2, 2), (64, 8, 3, 6), (5, 1, 1, 5)])
 def test_router_choice(E, count, keep, top):
     from aien_sovereign_core_mv_b200 import kernels as K
@@ -241,11 +278,12 @@ def test_router_choice(E, count, keep, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T", [3, 70])
-@pytest.mark.parametrize("shared", [0, 56])
-def test_routed_feed_forward_part(dtype, T, shared):
+@pytest.mark.parametrize("T", [3, 70, 400])
+@pytest.mark.parametrize("shared,D,F,E,top", [(0, 96, 40, 8, 3), (56, 96, 40, 8, 3), (64, 256, 256, 8, 3), (0, 128, 72, 16, 2)])
+def test_routed_feed_forward_part(dtype, T, shared, D, F, E, top):
+    """Sizes that take the plain products, the products that stream a few tokens' experts (width and
+    hidden size multiples of 256, few tokens) and the grouped tensor-core products (many tokens)."""
     from aien_sovereign_core_mv_b200.registry import make_part
-    D, F, E, top = 96, 40, 8, 3
     ff = make_part("feed_forward", "routed_experts", hidden_size=D, expert_ff=F, num_experts=E, top=top, group_count=4, group_keep=2,
                    shared_ff=shared)
     g = torch.Generator().manual_seed(T + shared)
