@@ -58,6 +58,77 @@ branch_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_pa
     }
 }
 
+// The same for rows of whole float4 vectors (H % 4 == 0, 16-byte aligned rows): every thread owns up
+// to BN_VECS vectors of the row, keeps their sums in registers between the passes, and has all the
+// loads of a pass in flight at once; the CTA has as many threads as the row has vectors (up to 512),
+// so a step of few rows still spreads a row's loads over many threads.  Parts are added in the order
+// of the plain kernel above; the sum of squares has a fixed order of its own.  Which of the two
+// kernels a row takes follows from H alone, never from the step.
+constexpr int BN_VECS = 4;
+
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
+template <typename T>
+__device__ __forceinline__ float4 parts_sum4(const T* __restrict__ p, int nparts, size_t part_stride, size_t idx) {
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int i = 0; i < nparts; ++i) d = f4_add(d, ld_act4(p + (size_t)i * part_stride + idx));
+    return d;
+}
+
+__device__ __forceinline__ void store_h4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store_h4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<uint32_t*>(&a);
+    r.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename TA, typename TB, typename TH>
+__global__ void __launch_bounds__(512)
+branch_norm_add_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_parts, size_t a_stride,
+                           const TB* __restrict__ b, int b_parts, size_t b_stride,
+                           const float* __restrict__ w, float eps, TH* __restrict__ h, int H) {
+    __shared__ float red[32];
+    griddep_launch();
+    const int nvec = H >> 2;
+    float4 wv[BN_VECS];
+#pragma unroll
+    for (int j = 0; j < BN_VECS; ++j) {                                   // the weights do not depend on the kernel ahead
+        const int v = threadIdx.x + j * blockDim.x;
+        wv[j] = v < nvec ? *reinterpret_cast<const float4*>(w + 4 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    griddep_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float4 y[BN_VECS], xv[BN_VECS];
+#pragma unroll
+    for (int j = 0; j < BN_VECS; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        y[j] = xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (v < nvec) {
+            xv[j] = __ldcg(reinterpret_cast<const float4*>(x + base) + v);
+            y[j] = parts_sum4(a, a_parts, a_stride, base + 4 * (size_t)v);
+            if (b != nullptr) y[j] = f4_add(y[j], parts_sum4(b, b_parts, b_stride, base + 4 * (size_t)v));
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < BN_VECS; ++j) ss += y[j].x * y[j].x + y[j].y * y[j].y + y[j].z * y[j].z + y[j].w * y[j].w;
+    const float total = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < BN_VECS; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) {
+            const float4 r = make_float4(xv[j].x + y[j].x * scale * wv[j].x, xv[j].y + y[j].y * scale * wv[j].y,
+                                         xv[j].z + y[j].z * scale * wv[j].z, xv[j].w + y[j].w * scale * wv[j].w);
+            *reinterpret_cast<float4*>(x + base + 4 * (size_t)v) = r;
+            if (h != nullptr) store_h4(h + base + 4 * (size_t)v, r);
+        }
+    }
+}
+
 // x[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w in place (the norm of the embedding row), h as above.
 template <typename TH>
 __global__ void __launch_bounds__(BN_THREADS)
@@ -91,6 +162,19 @@ AIEN_API int aien_branch_norm_add(float* x, const void* a, int a_dt, int a_parts
     if (T <= 0) return 0;
     if (H <= 0 || a == nullptr || a_parts < 1 || (b != nullptr && b_parts < 1)) return AIEN_E_SHAPE;
     if ((a_parts > 1 && a_dt != AIEN_DT_F32) || (b != nullptr && b_parts > 1 && b_dt != AIEN_DT_F32)) return AIEN_E_DTYPE;
+    {
+        const int nvec = H >> 2;
+        const int threads = nvec >= 512 ? 512 : ((nvec + 31) & ~31);
+        const bool aligned = (H & 3) == 0 && w_dt == AIEN_DT_F32 && threads > 0 && nvec <= threads * BN_VECS &&
+                             (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w | (uintptr_t)h) & 15) == 0 &&
+                             (a_stride & 3) == 0 && (b_stride & 3) == 0;
+        if (aligned) {
+            AIEN_DISPATCH_DTYPE(a_dt, TA, AIEN_DISPATCH_DTYPE(b_dt, TB, AIEN_DISPATCH_DTYPE(h_dt, TH,
+                (launch_chain(branch_norm_add_vec_kernel<TA, TB, TH>, dim3(T), dim3(threads), 0, stream,
+                              x, (const TA*)a, a_parts, a_stride, (const TB*)b, b_parts, b_stride, (const float*)w, eps, (TH*)h, H)))));
+            return launch_status();
+        }
+    }
     AIEN_DISPATCH_DTYPE(a_dt, TA, AIEN_DISPATCH_DTYPE(b_dt, TB, AIEN_DISPATCH_DTYPE(h_dt, TH,
         (launch_chain(branch_norm_add_kernel<TA, TB, TH>, dim3(T), dim3(BN_THREADS), 0, stream,
                       x, (const TA*)a, a_parts, a_stride, (const TB*)b, b_parts, b_stride, w, w_dt, eps, (TH*)h, H)))));

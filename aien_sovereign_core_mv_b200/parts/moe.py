@@ -56,7 +56,10 @@ class RoutedExperts(FeedForward):
         return shapes
 
     def bind(self, tensors):
-        self.w_router = tensors["router"].float().contiguous()          # the router is float32
+        # Router logits are float32 sums.  A float32 engine keeps the matrix in float32 and multiplies on the CUDA
+        # cores; a bfloat16 engine multiplies the stored bfloat16 matrix by the bfloat16 copy of the stream on the
+        # products it uses everywhere (every product of two bfloat16 numbers is exact in float32; the sums are float32).
+        self.w_router = tensors["router"].contiguous()
         ups = [tensors[f"experts.{e}.up"] for e in range(self.num_experts)]
         downs = [tensors[f"experts.{e}.down"] for e in range(self.num_experts)]
         if len({t.dtype for t in ups + downs}) > 1:
@@ -76,8 +79,11 @@ class RoutedExperts(FeedForward):
     def forward(self, ctx: StepContext, h: torch.Tensor):
         T, top = ctx.num_tokens, self.top
         ws = ctx.workspace
-        z = ws.take((T, self.num_experts), torch.float32)
-        K.gemm_simple(h, self.w_router, z)                              # float32 accumulation, float32 weights
+        if h.dtype == torch.bfloat16 and self.w_router.dtype == torch.bfloat16:
+            z = linear(ctx, h, self.w_router, out_dtype=torch.float32)
+        else:
+            z = ws.take((T, self.num_experts), torch.float32)
+            K.gemm_simple(h, self.w_router, z)                          # float32 operands, float32 sums
         ids = ws.take((T, top), torch.int32)
         wts = ws.take((T, top), torch.float32)
         K.moe_route(z, self.group_count, self.group_keep, top, self.renormalise, ids, wts)
