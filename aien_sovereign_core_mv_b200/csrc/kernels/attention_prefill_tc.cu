@@ -95,7 +95,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, int num_tiles, __nv_bfloat16* __restrict__ out, long out_stride,
                   int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta, int big_boxes,
-                  int nsplit, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                  int nsplit, float* __restrict__ part_o, float* __restrict__ part_ml, int chunk, const float* __restrict__ sinks) {
     using S = PtShape<HD>;
     extern __shared__ uint8_t pt_smem[];
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
@@ -128,7 +128,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int rows = min(PT_BM, q_len - q0);
     const int pos0 = ctx_len[s] - q_len + q0;                      // position of the tile's first query
     const int pos_last = pos0 + rows - 1;
-    const int first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    // chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0);
+    // the tile's first row has the earliest chunk, so no block before it is fetched, and every row masks what lies
+    // before its own chunk like the far edge of a window
+    const int first = max((window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0, chunk > 0 ? (pos0 / chunk) * chunk : 0);
     const int kb_first = first / PT_BN, kb_last = pos_last / PT_BN;
     const int per_split = (kb_last - kb_first + nsplit) / nsplit;         // ranges of whole blocks, in order: what a range holds
     const int kb_begin = kb_first + split * per_split;                   // depends on the tile's keys and nsplit alone
@@ -316,7 +319,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // one head alone alternates between two score regions and two probability buffers (h is 0 then)
         const uint32_t tS_base = tS0 + h * PT_BN + lane_off, tO = tO0 + h * HD + lane_off;
         const int hi = r < rows ? pos0 + r : -1;                                 // last key this row sees
-        const int lo = (window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+        const int lo = max((window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0, (chunk > 0 && hi > 0) ? (hi / chunk) * chunk : 0);
         // m_ref: the maximum the exponentials are taken against.  It follows the row's running
         // maximum only when that has grown by more than 8 (a factor 256, harmless in float32 and
         // in bfloat16's exponent), so the output in tensor memory is rescaled rarely.
@@ -428,6 +431,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     *reinterpret_cast<uint4*>(dstf + c0 + d) = make_uint4(o[d], o[d + 1], o[d + 2], o[d + 3]);
             }
         } else {
+        // a sink joins the denominator once, against the same reference as the sums (log2 units); no key, no value
+        if (sinks != nullptr && m_ref != -INFINITY) l_run += ex2_approx(sinks[head_a + h] * 1.4426950408889634f - m_ref);
         const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
         __nv_bfloat16* dst = out + (size_t)(qs + q0 + (r < rows ? r : 0)) * out_stride + (size_t)(head_a + h) * HD;
 #pragma unroll 1
@@ -523,8 +528,14 @@ template <int HD>
 static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMaps& mv, int big_boxes, const int* bt, int max_blocks,
                              const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
                              void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale, int cache_rows,
-                             void* scratch, long scratch_bytes, int max_ctx, int force_splits, cudaStream_t stream) {
+                             void* scratch, long scratch_bytes, int max_ctx, int force_splits, int chunk, const float* sinks,
+                             cudaStream_t stream) {
     auto kern = prefill_tc_kernel<HD>;
+    if (chunk > 0 || sinks != nullptr) {           // a chunk bounds the keys of a tile, and the merge of key ranges knows no sink
+        if (force_splits > 1) return AIEN_E_SHAPE;
+        scratch = nullptr;
+        scratch_bytes = 0;
+    }
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PtShape<HD>::SMEM) != cudaSuccess) return AIEN_E_STATE;
@@ -569,7 +580,7 @@ static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMa
     float* part_ml = nsplit > 1 ? part_o + part_rows * nsplit * HD : nullptr;
     launch_chain(kern, dim3((unsigned)ctas), dim3(PT_THREADS), (size_t)PtShape<HD>::SMEM, stream, mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                                                                      (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
-                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes, nsplit, part_o, part_ml);
+                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes, nsplit, part_o, part_ml, chunk, sinks);
     if (launch_status() != 0) return launch_status();
     if (nsplit > 1)
         launch_chain(prefill_merge_splits_kernel<HD>, dim3((unsigned)(part_rows / 8)), dim3(256), (size_t)0, stream, (const float*)part_o, (const float*)part_ml,
@@ -592,12 +603,15 @@ AIEN_API int aien_paged_attention_prefill_tc_supports(int hd, int page_size) {
 // scratch (may be null), scratch_bytes: room for the partial results of key ranges, num_tiles * 128 * nq *
 // splits * (hd + 2) floats; max_ctx: an upper bound of the contexts in ctx_len, known to the host;
 // force_splits: 0 lets the launch choose, n > 0 asks for n ranges (refused if the scratch is too small).
-AIEN_API int aien_paged_attention_prefill_tc_split(
+// chunk > 0: a query sees only the keys of its own chunk of that many positions; sinks (float32 [nq], may be null):
+// one more term exp(sink) in every head's softmax denominator.  With either, every tile's keys stay in one range.
+AIEN_API int aien_paged_attention_prefill_tc_masked(
     const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
     int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
     long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, void* scratch, long scratch_bytes, int max_ctx,
-    int force_splits, cudaStream_t stream) {
+    int force_splits, int chunk, const float* sinks, cudaStream_t stream) {
     if (num_tiles <= 0) return 0;
+    if (chunk < 0) return AIEN_E_SHAPE;
     if (!aien_paged_attention_prefill_tc_supports(hd, page_size) || nkv <= 0 || nq % nkv != 0 || q_rows <= 0 || cache_rows <= 0)
         return AIEN_E_SHAPE;
     if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
@@ -624,9 +638,19 @@ AIEN_API int aien_paged_attention_prefill_tc_split(
     if (!big_boxes) { mk.blk = mk.m[0]; mv.blk = mv.m[0]; }
     if (hd == 64)
         return launch_prefill_tc<64>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
-                                     nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, stream);
+                                     nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, stream);
     return launch_prefill_tc<128>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
-                                  nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, stream);
+                                  nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, stream);
+}
+
+AIEN_API int aien_paged_attention_prefill_tc_split(
+    const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
+    int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
+    long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, void* scratch, long scratch_bytes, int max_ctx,
+    int force_splits, cudaStream_t stream) {
+    return aien_paged_attention_prefill_tc_masked(q, q_stride, q_rows, k_cache, v_cache, cache_rows, block_table, max_blocks, q_start, ctx_len,
+                                                  tile_seq, tile_q0, num_tiles, out, out_stride, nq, nkv, hd, page_size, window, scale,
+                                                  scratch, scratch_bytes, max_ctx, force_splits, 0, nullptr, stream);
 }
 
 // The same without scratch: every tile's keys in one range.

@@ -151,6 +151,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_prefill_tc": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P],
         "aien_paged_attention_prefill_tc_split": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, P],
         "aien_paged_attention_prefill_tc_supports": [I, I],
+        "aien_paged_attention_prefill_tc_masked": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
@@ -980,12 +981,12 @@ def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
     v2 = v_cache.view(-1, num_kv_heads, value_dim)
     if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and value_dim == head_dim
             and prefill_attention_supports(q, k2, out, head_dim)):
-        # portions go through the tiled tensor-core kernel, which skips the key blocks outside a warp's chunk;
-        # the single tokens beside them through the plain kernel
+        # portions go through the tiled tensor-core kernels (tcgen05 for heads of 64 or 128, else mma.sync), which
+        # visit only the key blocks that a tile's chunks reach; the single tokens beside them through the plain kernel
         tile_seq, tile_q0, n = ctx.prefill_tiles
         if n > 0:
             paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
-                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, impl="mma",
+                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
                                     chunk=chunk, sinks=sinks)
         tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
         if nd > 0:
@@ -1035,11 +1036,9 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
     tcgen05 kernel cut the keys of a step with few tiles into ranges that run on separate SMs;
     ``splits`` > 0 asks for that many ranges (tests).  ``chunk`` > 0 (a query sees only the keys of
     its own chunk of that many positions) and ``sinks`` (float32 [heads], one more term exp(sink) in
-    the softmax denominator) are the mma.sync kernel's."""
+    the softmax denominator): both kernels take them; the tcgen05 kernel then keeps every tile's keys in one range."""
     _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out, sinks)
-    if chunk or sinks is not None:
-        impl = "mma"
-        assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
     for t in (block_table, q_start, ctx_len, tile_seq, tile_q0):
@@ -1049,11 +1048,12 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
         if scratch is not None:
             _dev(scratch)
             assert scratch.dtype == torch.float32 and scratch.is_contiguous()
-        _check(lib().aien_paged_attention_prefill_tc_split(
+        _check(lib().aien_paged_attention_prefill_tc_masked(
             _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), max_blocks, _p(q_start),
             _p(ctx_len), _p(tile_seq), _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim,
             page_size, window, float(scale), _p(scratch) if scratch is not None else None,
-            scratch.numel() * 4 if scratch is not None else 0, int(max_ctx), int(splits), _stream()), "paged_attention_prefill_tc")
+            scratch.numel() * 4 if scratch is not None else 0, int(max_ctx), int(splits), int(chunk), _p(sinks), _stream()),
+            "paged_attention_prefill_tc")
         return
     _check(lib().aien_paged_attention_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(q_start), _p(ctx_len), _p(tile_seq),

@@ -223,11 +223,13 @@ def test_attention_sees_its_chunk_and_the_sink(dtype, chunk, page, hd, hdv, nq, 
     assert float((out2.float() - out.float()).abs().max()) > 0.05
 
 
+@pytest.mark.parametrize("impl", ["tc", "mma"])
 @pytest.mark.parametrize("chunk,page,hd,nq,nkv,offset,qlen", [(24, 16, 32, 4, 2, 0, 150), (64, 16, 64, 6, 1, 37, 300), (128, 32, 128, 2, 1, 200, 129),
-                                                              (100, 16, 48, 3, 3, 99, 2), (16, 16, 64, 2, 2, 15, 131)])
-def test_tiled_prefill_attention_sees_its_chunk_and_the_sink(chunk, page, hd, nq, nkv, offset, qlen):
+                                                              (100, 16, 48, 3, 3, 99, 2), (16, 16, 64, 2, 2, 15, 131), (1000, 16, 128, 4, 2, 700, 520),
+                                                              (300, 16, 64, 3, 1, 1, 400)])
+def test_tiled_prefill_attention_sees_its_chunk_and_the_sink(chunk, page, hd, nq, nkv, offset, qlen, impl):
     """A portion of ``qlen`` queries that starts at position ``offset`` of its request, through the
-    tensor-core kernel: the keys at every chunk's two edges stand out, so a warp that skips a block
+    tensor-core kernels (tcgen05 where the head size allows, else and on request mma.sync): the keys at every chunk's two edges stand out, so a warp that skips a block
     it needs, or a row that sees across its chunk's edge, shows."""
     from aien_sovereign_core_mv_b200 import kernels as K
     g = torch.Generator().manual_seed(chunk * 3 + hd)
@@ -254,7 +256,7 @@ def test_tiled_prefill_attention_sees_its_chunk_and_the_sink(chunk, page, hd, nq
     qfull = torch.zeros(3 + qlen, nq * hd, dtype=torch.bfloat16)
     qfull[3:] = q.reshape(qlen, -1)
     K.paged_attention_prefill(qfull.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), mb, i32([0, 3, 3 + qlen]), i32([3, n]), i32([1] * len(tiles)),
-                              i32(tiles), len(tiles), out, nq, nkv, hd, page, 0, scale, chunk=chunk, sinks=sinks.cuda())
+                              i32(tiles), len(tiles), out, nq, nkv, hd, page, 0, scale, chunk=chunk, sinks=sinks.cuda(), impl=impl)
     want = pd.chunk_sink_attention(q.double().numpy(), keys.double().numpy(), vals.double().numpy(), qpos, list(range(n)), scale, chunk,
                                    sinks.double().numpy())
     H.assert_close(out[3:].float().cpu().numpy().reshape(qlen, nq, hd), want, 2e-2, "tiled attention")
