@@ -103,7 +103,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               const int* __restrict__ token_list, float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                               __nv_bfloat16* __restrict__ out, long out_stride,
                               int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes,
-                              FusedQK fq) {
+                              FusedQK fq, int kchunk, const float* __restrict__ sinks) {
     constexpr int NH = NT * 8;
     extern __shared__ float smem[];
     __shared__ int s_slot[AD_CHUNK];
@@ -113,10 +113,17 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     const int g = lane >> 2, c = lane & 3;
     // blockIdx.z counts the tokens this launch serves: all tokens of the step, or those named by
     // token_list (the single-token requests of a mixed step).  Scratch is indexed by blockIdx.z.
-    const int split = blockIdx.x, kvh = blockIdx.y, zt = blockIdx.z;
+    const int kvh = blockIdx.y, zt = blockIdx.z;
     const int t = token_list ? token_list[zt] : zt;
     const int G = nq / nkv;
     const int pos = positions[t];
+    // kchunk > 0: the token sees only the keys of its own chunk of kchunk positions (counted from position 0).
+    // The launch then has only as many key blocks as a chunk can touch, and blockIdx.x counts them from the
+    // block that holds the chunk's first key; the partial results are indexed the same way.
+    int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (kchunk > 0) first = max(first, (pos / kchunk) * kchunk);
+    const int psplit = blockIdx.x;                                  // where this block's partial results go
+    const int split = kchunk > 0 ? first / AD_CHUNK + (int)blockIdx.x : (int)blockIdx.x;
     // In a decode-only step token t is request t (seq_of_token may be null): the table row does not
     // hang on another load, so the page lookups go out together with the position load.
     const int* bt = block_table + (size_t)(seq_of_token ? seq_of_token[t] : t) * max_blocks;
@@ -128,7 +135,6 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
         const int pg = pi < max_blocks ? bt[pi] : -1;
         s_slot[tid] = pg < 0 ? -1 : pg * page_size + key % page_size;
     }
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int lo = max(first, chunk_base), hi = min(pos, chunk_base + AD_CHUNK - 1);
     if (lo > hi) return;
     __syncthreads();
@@ -307,14 +313,14 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
             for (int e = 0; e < 2; ++e) {
                 const int h = nt * 8 + 2 * c + e;
                 if (h < G) {
-                    const size_t row = ((size_t)zt * nq + kvh * G + h) * max_splits + split;
+                    const size_t row = ((size_t)zt * nq + kvh * G + h) * max_splits + psplit;
                     part_out[row * hd + mt * 16 + g] = oacc[nt][e];
                     part_out[row * hd + mt * 16 + g + 8] = oacc[nt][2 + e];
                 }
             }
     }
     if (tid < G) {
-        const size_t row = ((size_t)zt * nq + kvh * G + tid) * max_splits + split;
+        const size_t row = ((size_t)zt * nq + kvh * G + tid) * max_splits + psplit;
         part_ml[row * 2] = Hm[tid];
         part_ml[row * 2 + 1] = Hl[tid];
     }
@@ -331,12 +337,14 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    const int part_lo = kchunk > 0 ? 0 : s_lo;                      // index of the first block's partial results
+    const float* hs = sinks != nullptr ? sinks + kvh * G : nullptr;
     if (hd <= 128)
         ad_merge_chunks<NH, 1>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
-                               G, hd, max_splits, s_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); });
+                               G, hd, max_splits, part_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); }, hs);
     else
         ad_merge_chunks<NH, 2>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
-                               G, hd, max_splits, s_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); });
+                               G, hd, max_splits, part_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); }, hs);
 }
 
 template <int HS, int NT>
@@ -344,7 +352,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          const int* seq_of_token, const int* positions, const int* token_list, float* part_out, float* part_ml, int* counters,
                          void* out, long out_stride,
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-                         const FusedQK& fq, cudaStream_t stream) {
+                         const FusedQK& fq, int kchunk, const float* sinks, cudaStream_t stream) {
     const int NH = NT * 8;
     size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;          // scores, max/denominator, probabilities
     if (fq.k != nullptr) loop_bytes += (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;      // fused q/k scratch, q
@@ -370,7 +378,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
     kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                  (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions, token_list,
                  part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits,
-                 misc_bytes, fq);
+                 misc_bytes, fq, kchunk, sinks);
     return launch_status();
 }
 
@@ -386,7 +394,22 @@ static int decode_dispatch(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
     float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-    const FusedQK& fq, cudaStream_t stream);
+    const FusedQK& fq, cudaStream_t stream, int kchunk = 0, const float* sinks = nullptr);
+
+// The same under a chunk mask (kchunk > 0: a token sees only the keys of its own chunk of that many positions) and
+// with per-head softmax sinks (float32 [nq], may be null).  With kchunk > 0, max_splits counts the key blocks a
+// chunk can touch, ceil(kchunk / 128) + 1 at most (and no more than the longest context has), not those of the context.
+AIEN_API int aien_paged_attention_decode_masked(
+    const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+    const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
+    float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
+    int kchunk, const float* sinks, cudaStream_t stream) {
+    if (kchunk < 0) return AIEN_E_SHAPE;
+    FusedQK none = {};
+    return decode_dispatch(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, token_list, out,
+                           out_stride, part_out, part_ml, counters, nq, nkv, hd, page_size, window, scale, max_splits, T, none, stream,
+                           kchunk, sinks);
+}
 
 AIEN_API int aien_paged_attention_decode(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
@@ -416,7 +439,7 @@ static int decode_dispatch(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
     float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-    const FusedQK& fq, cudaStream_t stream) {
+    const FusedQK& fq, cudaStream_t stream, int kchunk, const float* sinks) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 256 || (hd & 15) || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_splits <= 0) return AIEN_E_SHAPE;
     const int G = nq / nkv;
@@ -428,7 +451,7 @@ static int decode_dispatch(
     if (HS == hs && NT == nt)                                                                                        \
         rc = launch_decode<hs, nt>(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions,  \
                                    token_list, part_out, part_ml, counters, out, out_stride, nq, nkv, hd, page_size, window, scale,        \
-                                   max_splits, T, fq, stream);
+                                   max_splits, T, fq, kchunk, sinks, stream);
     AD_CASE(1, 1) AD_CASE(2, 1) AD_CASE(3, 1) AD_CASE(4, 1) AD_CASE(5, 1) AD_CASE(6, 1) AD_CASE(7, 1) AD_CASE(8, 1)
     AD_CASE(1, 2) AD_CASE(2, 2) AD_CASE(3, 2) AD_CASE(4, 2) AD_CASE(5, 2) AD_CASE(6, 2) AD_CASE(7, 2) AD_CASE(8, 2)
 #undef AD_CASE

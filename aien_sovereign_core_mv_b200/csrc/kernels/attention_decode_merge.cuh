@@ -33,7 +33,8 @@ __host__ __device__ inline size_t ad_merge_scratch_floats(int max_splits, int G,
 template <int NH, int PER, typename Sync>
 __device__ __forceinline__ void ad_merge_chunks(float* scratch, const float* __restrict__ part_out, const float* __restrict__ part_ml,
                                                 __nv_bfloat16* __restrict__ out_row, size_t row0, int G, int hd, int max_splits,
-                                                int s_lo, int nsp, int tid, int nthreads, Sync sync) {
+                                                int s_lo, int nsp, int tid, int nthreads, Sync sync,
+                                                const float* __restrict__ sinks = nullptr) {
     float* Fi = scratch;                                 // [G]: 1 / total denominator
     float* Fm = Fi + ad_merge_round4((size_t)G);         // [nsp][G]: chunk max, then the chunk's weight
     float* Fl = Fm + ad_merge_round4((size_t)max_splits * G);   // [nsp][G]: chunk denominator; later [AD_MERGE_WAYS][hd]: the series' sums
@@ -52,6 +53,9 @@ __device__ __forceinline__ void ad_merge_chunks(float* scratch, const float* __r
         for (int sp = lane; sp < nsp; sp += 32) M = fmaxf(M, Fm[sp * G + h]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        // sinks[h] (when given): one more term exp(sink) in the head's denominator, with no key and no value
+        const float sink = sinks != nullptr ? sinks[h] : -INFINITY;
+        M = fmaxf(M, sink);
         float L = 0.f;
         for (int sp = lane; sp < nsp; sp += 32) {
             const float ms = Fm[sp * G + h];
@@ -61,6 +65,7 @@ __device__ __forceinline__ void ad_merge_chunks(float* scratch, const float* __r
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        if (sink != -INFINITY) L += expf(sink - M);
         if (lane == 0) Fi[h] = L > 0.f ? 1.0f / L : 0.f;
     }
     sync();                                              // the denominators are used up: their place takes the series' sums

@@ -155,19 +155,19 @@ stream_norm_inplace_kernel(float* __restrict__ x, const void* __restrict__ w, in
 
 using namespace aien;
 
-// a_dt / b_dt: dtype of the sources (float32 when they have several parts); h_dt: dtype of h.
+// a_dt / b_dt: dtype of the sources (parts of either dtype are added in float32); h_dt: dtype of h.
 AIEN_API int aien_branch_norm_add(float* x, const void* a, int a_dt, int a_parts, size_t a_stride,
                                   const void* b, int b_dt, int b_parts, size_t b_stride,
                                   const void* w, int w_dt, float eps, void* h, int h_dt, int T, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || a == nullptr || a_parts < 1 || (b != nullptr && b_parts < 1)) return AIEN_E_SHAPE;
-    if ((a_parts > 1 && a_dt != AIEN_DT_F32) || (b != nullptr && b_parts > 1 && b_dt != AIEN_DT_F32)) return AIEN_E_DTYPE;
     {
         const int nvec = H >> 2;
         const int threads = nvec >= 512 ? 512 : ((nvec + 31) & ~31);
         const bool aligned = (H & 3) == 0 && w_dt == AIEN_DT_F32 && threads > 0 && nvec <= threads * BN_VECS &&
                              (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w | (uintptr_t)h) & 15) == 0 &&
-                             (a_stride & 3) == 0 && (b_stride & 3) == 0;
+                             (a_stride & 3) == 0 && (b_stride & 3) == 0 &&
+                             (a_dt == AIEN_DT_F32 || ((uintptr_t)a & 7) == 0) && (b == nullptr || b_dt == AIEN_DT_F32 || ((uintptr_t)b & 7) == 0);
         if (aligned) {
             AIEN_DISPATCH_DTYPE(a_dt, TA, AIEN_DISPATCH_DTYPE(b_dt, TB, AIEN_DISPATCH_DTYPE(h_dt, TH,
                 (launch_chain(branch_norm_add_vec_kernel<TA, TB, TH>, dim3(T), dim3(threads), 0, stream,

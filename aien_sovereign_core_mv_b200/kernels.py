@@ -153,6 +153,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_prefill_tc_supports": [I, I],
         "aien_paged_attention_prefill_tc_masked": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
+        "aien_paged_attention_decode_masked": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, I, P, P],
         "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
         "aien_attention_decode_stream_error": [],
@@ -360,8 +361,12 @@ def _source(t: Optional[torch.Tensor], shape) -> tuple:
     """(pointer, dtype code, parts, part stride) of a branch output: [T,H], or float32 parts [P,T,H]."""
     if t is None:
         return 0, F32, 1, 0
-    n, stride = _parts_of(t, shape)
-    return _p(t), dt(t), n, stride
+    assert t.is_contiguous()
+    if t.dim() == 3:                         # parts [P,T,H], float32 or (the weighted outputs of routed experts) bfloat16
+        assert tuple(t.shape[1:]) == tuple(shape)
+        return _p(t), dt(t), t.shape[0], t.shape[1] * t.shape[2]
+    assert tuple(t.shape) == tuple(shape)
+    return _p(t), dt(t), 1, 0
 
 
 def branch_norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, b: Optional[torch.Tensor] = None,
@@ -488,8 +493,10 @@ def moe_grouped_supports(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tens
 
 
 def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
-                parts: torch.Tensor, top: int, act_kind: int) -> None:
-    """parts[c, t] = wts[t,c] * w_down[e] f(w_up[e] h[t]) with e = ids[t,c]: the chosen experts of every token.
+                top: int, act_kind: int) -> torch.Tensor:
+    """Returns parts [top, T, D] with parts[c, t] = wts[t,c] * w_down[e] f(w_up[e] h[t]), e = ids[t,c]: the chosen
+    experts of every token, weighted, one part per choice (float32; bfloat16 from the grouped products, whose
+    consumer adds them in float32).
     bfloat16: a few tokens stream their experts' rows (one warp per output value, 16-byte loads); larger
     steps sort the (token, choice) pairs by expert and run two grouped tcgen05 products, the activation in
     the first one's epilogue, the weights and the way back to token order in the second's.  float32, and
@@ -498,14 +505,16 @@ def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, 
     E, Fd, _ = w_up.shape
     ws = ctx.workspace
     ok = _MOE_IMPL != "plain" and moe_grouped_supports(h, w_up, w_down)
+    grouped = ok and T > MOE_ROWS_MAX_TOKENS
+    parts = ws.take((top, T, D), torch.bfloat16 if grouped else torch.float32)
     if ok and T <= MOE_ROWS_MAX_TOKENS and D % 256 == 0 and Fd % 256 == 0:
         act = ws.take((T * top, Fd), torch.bfloat16)
         _check(lib().aien_moe_expert_rows_bf16(0, _p(h), h.stride(0), _p(w_up), _p(ids), _p(wts), _p(act), T, top, Fd, D,
                                                int(act_kind), _stream()), "moe_expert_rows(up)")
         _check(lib().aien_moe_expert_rows_bf16(1, _p(act), Fd, _p(w_down), _p(ids), _p(wts), _p(parts), T, top, D, Fd,
                                                int(act_kind), _stream()), "moe_expert_rows(down)")
-        return
-    if ok and T > MOE_ROWS_MAX_TOKENS:
+        return parts
+    if grouped:
         tiles = _moe_tiles(T * top, E)
         rows = tiles * 128
         tile_group = ws.take((tiles,), torch.int32)
@@ -519,12 +528,13 @@ def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, 
         _check(lib().aien_moe_gather_rows(_p(h), h.stride(0), _p(row_pair), top, _p(a_sorted), D, rows, _stream()), "moe_gather_rows")
         _check(lib().aien_gemm_tc_grouped(_p(a_sorted), D, _p(w_up), D, E, _p(act), BF16, Fd, _p(tile_group), tiles, None, None,
                                           Fd, D, 2 + int(act_kind), _stream()), "gemm_tc_grouped(up)")
-        _check(lib().aien_gemm_tc_grouped(_p(act), Fd, _p(w_down), Fd, E, _p(parts), F32, D, _p(tile_group), tiles, _p(row_dest),
+        _check(lib().aien_gemm_tc_grouped(_p(act), Fd, _p(w_down), Fd, E, _p(parts), BF16, D, _p(tile_group), tiles, _p(row_dest),
                                           _p(row_scale), D, Fd, 0, _stream()), "gemm_tc_grouped(down)")
-        return
+        return parts
     act = ws.take((T * top, Fd), ctx.dtype)
     moe_expert_up(h, w_up, ids, act, top, act_kind)
     moe_expert_down(act, w_down, ids, wts, parts, top)
+    return parts
 
 
 def act_rows(a: torch.Tensor, act_kind: int) -> None:
@@ -851,13 +861,16 @@ def decode_stream_supports(num_q_heads: int, num_kv_heads: int, head_dim: int, p
 
 def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, out,
                            part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
-                           max_splits, token_list=None, num_tokens=None, impl: Optional[str] = None) -> None:
+                           max_splits, token_list=None, num_tokens=None, impl: Optional[str] = None, chunk: int = 0,
+                           sinks: Optional[torch.Tensor] = None) -> None:
     """Split-key decode attention; the CTA that finishes last merges the chunks.  The ticket
     counters are one small device buffer that every launch finds zero and leaves zero.
     ``impl``: "stream" (TMA ring, persistent CTAs; where the sizes allow) or "direct" (one CTA per
-    chunk); both give the same bits.  Default from ``AIEN_B200_DECODE_ATTENTION``, else "stream"."""
+    chunk); both give the same bits.  Default from ``AIEN_B200_DECODE_ATTENTION``, else "stream".
+    ``chunk`` > 0 (a token sees only the keys of its own chunk of that many positions; ``max_splits`` then counts
+    the 128-key blocks a chunk can touch, see decode_splits) and ``sinks`` (float32 [heads]) are the direct kernel's."""
     global _ticket_counters
-    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml)
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml, sinks)
     # seq_of_token None: token t belongs to row t of the block table.  token_list: serve only these tokens.
     T = q.shape[0] if token_list is None else int(num_tokens)
     if _ticket_counters is None:
@@ -868,6 +881,13 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
     assert part_out.dtype == torch.float32 and part_out.numel() >= T * num_q_heads * max_splits * head_dim
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
     impl = impl or _DECODE_ATTN_IMPL
+    if chunk or sinks is not None:
+        assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
+        _check(lib().aien_paged_attention_decode_masked(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
+            _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
+            page_size, window, float(scale), max_splits, T, int(chunk), _p(sinks), _stream()), "paged_attention_decode_masked")
+        return
     if impl == "stream" and decode_stream_supports(num_q_heads, num_kv_heads, head_dim, page_size, max_splits):
         _check(lib().aien_paged_attention_decode_stream(
             _p(q), q.stride(0), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), max_blocks, _p(seq_of_token),
@@ -966,9 +986,16 @@ def paged_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale)
 
 
-def chunk_attention_workspace_bytes(lim, num_heads: int, value_dim: int, key_span: int) -> int:
-    """Scratch of attention under a chunk mask for the largest step: a token sees at most ``key_span`` keys."""
-    return 4096
+def decode_splits(max_ctx: int, chunk: int) -> int:
+    """Key blocks of 128 that the split-key decode kernel runs per token: those of the longest context, or,
+    under a chunk mask, those a chunk can touch."""
+    splits = max(1, (max_ctx + DECODE_CHUNK - 1) // DECODE_CHUNK)
+    return min(splits, (chunk + DECODE_CHUNK - 1) // DECODE_CHUNK + 1) if chunk > 0 else splits
+
+
+def chunk_attention_workspace_bytes(lim, num_heads: int, value_dim: int, chunk: int) -> int:
+    """Scratch of attention under a chunk mask for the largest step: the partial results of the split-key kernel."""
+    return lim.max_seqs * num_heads * decode_splits(lim.max_context, chunk) * (value_dim + 2) * 4 + 4096
 
 
 def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor,
@@ -979,6 +1006,21 @@ def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
     per-head softmax sink; values of size ``value_dim``.  Picks the kernel for the step."""
     k2 = k_cache.view(-1, num_kv_heads, head_dim)
     v2 = v_cache.view(-1, num_kv_heads, value_dim)
+    split_key = (_FORCE_ATTN != "generic" and value_dim == head_dim
+                 and decode_attention_supports(q, k2, num_q_heads, num_kv_heads, head_dim) and out.dtype == torch.bfloat16)
+
+    def single_tokens(tokens, n):
+        """The tokens that come alone: the split-key kernel over the 128-key blocks their chunk touches."""
+        splits = decode_splits(ctx.max_ctx_len, chunk)
+        part_out = ctx.workspace.take((n * num_q_heads * splits * head_dim,), torch.float32)
+        part_ml = ctx.workspace.take((n * num_q_heads * splits * 2,), torch.float32)
+        paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, None if tokens is None else ctx.seq_of_token,
+                               ctx.positions, out, part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                               splits, token_list=tokens, num_tokens=n, impl="direct", chunk=chunk, sinks=sinks)
+
+    if ctx.decode_only and split_key:
+        single_tokens(None, q.shape[0])
+        return
     if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and value_dim == head_dim
             and prefill_attention_supports(q, k2, out, head_dim)):
         # portions go through the tiled tensor-core kernels (tcgen05 for heads of 64 or 128, else mma.sync), which
@@ -989,7 +1031,9 @@ def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
                                     out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
                                     chunk=chunk, sinks=sinks)
         tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
-        if nd > 0:
+        if nd > 0 and split_key:
+            single_tokens(tokens, nd)
+        elif nd > 0:
             paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                                     num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
                                     chunk=chunk, sinks=sinks, value_dim=value_dim, token_list=tokens, num_tokens=nd)

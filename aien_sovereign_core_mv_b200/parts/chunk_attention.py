@@ -80,19 +80,10 @@ class ChunkedSinkAttention(Mixer):
             return CacheNeed("window", self.window, planes)
         return CacheNeed("full", 0, planes)
 
-    def _key_span(self, lim_context: int) -> int:
-        """The most keys a token can see."""
-        span = lim_context
-        if self.chunk > 0:
-            span = min(span, self.chunk)
-        if self.window > 0:
-            span = min(span, self.window)
-        return max(1, span)
-
     def workspace_bytes(self, lim):
         rows = self.q_dim + self.k_dim + (0 if self.values_from_keys else self.v_dim)
         return lim.max_tokens * (rows * 4 + self.q_dim * lim.itemsize + self.o_in * lim.itemsize + self.hidden_size * 4) + 8192 \
-            + 2 * K.PARTIALS_MAX_BYTES + K.chunk_attention_workspace_bytes(lim, self.num_heads, self.value_dim, self._key_span(lim.max_context))
+            + 2 * K.PARTIALS_MAX_BYTES + K.chunk_attention_workspace_bytes(lim, self.num_heads, self.value_dim, self.chunk)
 
     # ---- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):

@@ -22,9 +22,9 @@ class RoutedExperts(FeedForward):
     tanh form ("gelu_tanh").  ``shared_ff`` > 0: one more expert of that hidden size runs for
     every token and is added.
 
-    ``forward`` returns ``(parts, shared)``: the weighted outputs of the chosen experts as float32
-    parts [top, T, H], one per choice, and the shared expert's output (or None); whoever takes the
-    branch adds them in that order.  Expert tensors are stacked [E, ...] when they arrive."""
+    ``forward`` returns ``(parts, shared)``: the weighted outputs of the chosen experts as parts
+    [top, T, H], one per choice (float32, or bfloat16 from the grouped tensor-core products), and
+    the shared expert's output (or None); whoever takes the branch adds them in that order, in float32.  Expert tensors are stacked [E, ...] when they arrive."""
 
     def __init__(self, hidden_size: int, expert_ff: int, num_experts: int, top: int, group_count: int = 1, group_keep: int = 1,
                  shared_ff: int = 0, act: str = "gelu", shared_act: Optional[str] = None, renormalise: bool = False):
@@ -87,8 +87,7 @@ class RoutedExperts(FeedForward):
         ids = ws.take((T, top), torch.int32)
         wts = ws.take((T, top), torch.float32)
         K.moe_route(z, self.group_count, self.group_keep, top, self.renormalise, ids, wts)
-        parts = ws.take((top, T, self.hidden_size), torch.float32)
-        K.moe_experts(ctx, h, self.w_up, self.w_down, ids, wts, parts, top, self.act)
+        parts = K.moe_experts(ctx, h, self.w_up, self.w_down, ids, wts, top, self.act)
         shared = None
         if self.shared_ff:
             a = linear(ctx, h, self.w_shared_up)

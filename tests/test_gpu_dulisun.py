@@ -262,6 +262,48 @@ def test_tiled_prefill_attention_sees_its_chunk_and_the_sink(chunk, page, hd, nq
     H.assert_close(out[3:].float().cpu().numpy().reshape(qlen, nq, hd), want, 2e-2, "tiled attention")
 
 
+@pytest.mark.parametrize("chunk,page,hd,nq,nkv", [(24, 16, 32, 4, 2), (64, 16, 64, 6, 1), (128, 32, 128, 2, 1), (100, 16, 48, 3, 3), (16, 16, 64, 2, 2),
+                                                  (1000, 16, 128, 8, 2), (300, 16, 64, 16, 1), (129, 8, 16, 2, 1)])
+def test_split_key_decode_attention_sees_its_chunk_and_the_sink(chunk, page, hd, nq, nkv):
+    """Single tokens at the first, second and last position of a chunk, next to every edge, through the
+    split-key kernel, whose blocks of 128 keys are counted from the block that holds the chunk's start."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(chunk * 5 + hd)
+    n = min(3 * chunk + 7, 2600)
+    keys = torch.randn(n, nkv, hd, generator=g)
+    vals = torch.randn(n, nkv, hd, generator=g)
+    for p in range(0, n, chunk):
+        keys[p] *= 3.0
+        if p > 0:
+            keys[p - 1] *= 3.0
+    edges = sorted({p for c in range(0, n, chunk) for p in (c - 1, c, c + 1, c + chunk // 2) if 0 <= p < n} | {0, n - 1, 127, 128} & set(range(n)))
+    T = len(edges)
+    q = torch.randn(T, nq, hd, generator=g).to(torch.bfloat16)
+    keys, vals = keys.to(torch.bfloat16), vals.to(torch.bfloat16)
+    sinks = torch.tensor([(-1.0) ** h * (0.5 + 0.7 * h) for h in range(nq)])
+    scale = 0.5 / math.sqrt(hd)
+    order = list(reversed(range((n + page - 1) // page + 1)))
+    kc, vc, row = _paged(keys, vals, page, order)
+    mb = len(row) + 2
+    bt = torch.full((2, mb), -1, dtype=torch.int32)
+    bt[1, :len(row)] = torch.tensor(row, dtype=torch.int32)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32).cuda()
+    splits = K.decode_splits(n, chunk)
+    part_out = torch.empty(T * nq * splits * hd, dtype=torch.float32).cuda()
+    part_ml = torch.empty(T * nq * splits * 2, dtype=torch.float32).cuda()
+    out = torch.zeros(T, nq * hd, dtype=torch.bfloat16).cuda()
+    K.paged_attention_decode(q.reshape(T, -1).cuda(), kc.cuda(), vc.cuda(), bt.cuda(), mb, i32([1] * T), i32(edges), out, part_out, part_ml,
+                             nq, nkv, hd, page, 0, scale, splits, impl="direct", chunk=chunk, sinks=sinks.cuda())
+    want = pd.chunk_sink_attention(q.double().numpy(), keys.double().numpy(), vals.double().numpy(), edges, list(range(n)), scale, chunk,
+                                   sinks.double().numpy())
+    H.assert_close(out.float().cpu().numpy().reshape(T, nq, hd), want, 2e-2, "split-key attention")
+    # a second launch finds the tickets at zero again and gives the same bits
+    out2 = torch.zeros_like(out)
+    K.paged_attention_decode(q.reshape(T, -1).cuda(), kc.cuda(), vc.cuda(), bt.cuda(), mb, i32([1] * T), i32(edges), out2, part_out, part_ml,
+                             nq, nkv, hd, page, 0, scale, splits, impl="direct", chunk=chunk, sinks=sinks.cuda())
+    assert torch.equal(out, out2)
+
+
 @pytest.mark.parametrize("E,count,keep,top", [(8, 4, 2, 3), (12, 2, 1, 2), (4, 1, 1, 1), (6, 6, 2, 2), (64, 8, 3, 6), (5, 1, 1, 5)])
 def test_router_choice(E, count, keep, top):
     from aien_sovereign_core_mv_b200 import kernels as K
