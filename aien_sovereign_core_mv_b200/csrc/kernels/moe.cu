@@ -144,7 +144,9 @@ moe_sort_pairs_kernel(const int* __restrict__ ids, const float* __restrict__ wts
                       int* __restrict__ tile_group, int* __restrict__ row_pair, int* __restrict__ row_dest,
                       float* __restrict__ row_scale) {
     __shared__ int count[ROUTE_MAX_EXPERTS];
-    __shared__ int start[ROUTE_MAX_EXPERTS];      // first row of the expert's run; then the cursor into it
+    __shared__ int start[ROUTE_MAX_EXPERTS];      // first row of the expert's run
+    __shared__ int cursor[ROUTE_MAX_EXPERTS];     // next free row of the run
+    __shared__ int used_rows;
     griddep_launch();
     griddep_wait();
     const int tid = threadIdx.x;
@@ -155,25 +157,27 @@ moe_sort_pairs_kernel(const int* __restrict__ ids, const float* __restrict__ wts
     if (tid == 0) {
         int row = 0;
         for (int e = 0; e < E; ++e) {
-            start[e] = row;
+            start[e] = cursor[e] = row;
             row += (count[e] + 127) & ~127;
         }
-        count[0] = row;                            // total rows in use, for the fill below
+        used_rows = row;
     }
     __syncthreads();
-    const int used_rows = count[0];
-    for (int i = tid; i < max_tiles; i += SORT_THREADS) tile_group[i] = -1;
-    for (int r = tid; r < max_tiles * 128; r += SORT_THREADS) { row_pair[r] = -1; row_dest[r] = -1; row_scale[r] = 0.f; }
-    __syncthreads();
+    // tiles of a run belong to its expert; tiles beyond the last run are empty, and their rows stay unwritten
+    // (the gather and the products look at tile_group first)
+    for (int i = (used_rows >> 7) + tid; i < max_tiles; i += SORT_THREADS) tile_group[i] = -1;
     for (int e = tid; e < E; e += SORT_THREADS) {
-        const int first = start[e] >> 7;
-        const int last = ((e + 1 < E ? start[e + 1] : used_rows) >> 7);
-        for (int i = first; i < last; ++i) tile_group[i] = e;
+        const int first = start[e] >> 7, n = (count[e] + 127) >> 7;
+        for (int i = 0; i < n; ++i) tile_group[first + i] = e;
     }
-    __syncthreads();
+    // the padding rows at the end of every run
+    for (int e = tid >> 7; e < E; e += SORT_THREADS >> 7) {
+        const int r = start[e] + count[e] + (tid & 127);
+        if (r < start[e] + ((count[e] + 127) & ~127)) { row_pair[r] = -1; row_dest[r] = -1; row_scale[r] = 0.f; }
+    }
     for (int p = tid; p < P; p += SORT_THREADS) {
         const int e = __ldcg(ids + p);
-        const int r = atomicAdd(&start[e], 1);
+        const int r = atomicAdd(&cursor[e], 1);
         const int t = p / top, c = p - t * top;
         row_pair[r] = p;
         row_dest[r] = c * T + t;
@@ -181,19 +185,32 @@ moe_sort_pairs_kernel(const int* __restrict__ ids, const float* __restrict__ wts
     }
 }
 
-// a_sorted[r, :] = h[row_pair[r] / top, :] (zeros in padding rows); bfloat16, 16-byte vectors, D % 8 == 0.
+// a_sorted[r, :] = h[row_pair[r] / top, :] (zeros in padding rows; rows of empty tiles are left alone); bfloat16,
+// 16-byte vectors, D % 8 == 0.  Four rows a CTA, 64 threads a row: the row's pair is looked up once and up to four
+// vectors of a thread are in flight together.
 __global__ void __launch_bounds__(256)
-moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, long h_stride, const int* __restrict__ row_pair, int top,
-                       __nv_bfloat16* __restrict__ a_sorted, int D, int rows) {
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, long h_stride, const int* __restrict__ row_pair,
+                       const int* __restrict__ tile_group, int top, __nv_bfloat16* __restrict__ a_sorted, int D, int rows) {
     griddep_launch();
     griddep_wait();
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 6), lane = threadIdx.x & 63;
+    if (r >= rows || __ldcg(tile_group + (r >> 7)) < 0) return;
+    const int p = __ldcg(row_pair + r);
     const int vec = D >> 3;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)rows * vec; i += (size_t)gridDim.x * blockDim.x) {
-        const int r = (int)(i / vec), v = (int)(i - (size_t)r * vec);
-        const int p = __ldcg(row_pair + r);
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (p >= 0) val = __ldcg(reinterpret_cast<const uint4*>(h + (size_t)(p / top) * h_stride) + v);
-        reinterpret_cast<uint4*>(a_sorted + (size_t)r * D)[v] = val;
+    const uint4* src = p >= 0 ? reinterpret_cast<const uint4*>(h + (size_t)(p / top) * h_stride) : nullptr;
+    uint4* dst = reinterpret_cast<uint4*>(a_sorted + (size_t)r * D);
+    for (int v0 = lane; v0 < vec; v0 += 256) {
+        uint4 val[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int v = v0 + 64 * j;
+            val[j] = (src != nullptr && v < vec) ? __ldcg(src + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int v = v0 + 64 * j;
+            if (v < vec) dst[v] = val[j];
+        }
     }
 }
 
@@ -317,13 +334,12 @@ AIEN_API int aien_moe_sort_pairs(const int* ids, const float* wts, int T, int to
     return launch_status();
 }
 
-AIEN_API int aien_moe_gather_rows(const void* h, long h_stride, const int* row_pair, int top, void* a_sorted, int D, int rows,
-                                  cudaStream_t stream) {
+AIEN_API int aien_moe_gather_rows(const void* h, long h_stride, const int* row_pair, const int* tile_group, int top, void* a_sorted,
+                                  int D, int rows, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (D <= 0 || (D & 7) || (h_stride & 7) || ((uintptr_t)h & 15) || ((uintptr_t)a_sorted & 15)) return AIEN_E_ALIGN;
-    const size_t n = (size_t)rows * (D >> 3);
-    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    launch_chain(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)h, h_stride, row_pair, top,
+    const int blocks = (rows + 3) / 4;
+    launch_chain(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)h, h_stride, row_pair, tile_group, top,
                  (__nv_bfloat16*)a_sorted, D, rows);
     return launch_status();
 }

@@ -126,7 +126,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_moe_expert_down": [P, I, P, I, P, P, P, I, I, I, I, P],
         "aien_act_rows": [P, I, c_size_t, I, P],
         "aien_moe_sort_pairs": [P, P, I, I, I, I, P, P, P, P, P],
-        "aien_moe_gather_rows": [P, L, P, I, P, I, I, P],
+        "aien_moe_gather_rows": [P, L, P, P, I, P, I, I, P],
         "aien_moe_expert_rows_bf16": [I, P, L, P, P, P, P, I, I, I, I, I, P],
         "aien_gemm_tc_grouped": [P, L, P, L, I, P, I, L, P, I, P, P, I, I, I, P],
         "aien_argmax_rows": [P, I, I, P, P],
@@ -525,7 +525,8 @@ def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, 
         act = ws.take((rows, Fd), torch.bfloat16)
         _check(lib().aien_moe_sort_pairs(_p(ids), _p(wts), T, top, E, tiles, _p(tile_group), _p(row_pair), _p(row_dest),
                                          _p(row_scale), _stream()), "moe_sort_pairs")
-        _check(lib().aien_moe_gather_rows(_p(h), h.stride(0), _p(row_pair), top, _p(a_sorted), D, rows, _stream()), "moe_gather_rows")
+        _check(lib().aien_moe_gather_rows(_p(h), h.stride(0), _p(row_pair), _p(tile_group), top, _p(a_sorted), D, rows, _stream()),
+               "moe_gather_rows")
         _check(lib().aien_gemm_tc_grouped(_p(a_sorted), D, _p(w_up), D, E, _p(act), BF16, Fd, _p(tile_group), tiles, None, None,
                                           Fd, D, 2 + int(act_kind), _stream()), "gemm_tc_grouped(up)")
         _check(lib().aien_gemm_tc_grouped(_p(act), Fd, _p(w_down), Fd, E, _p(parts), BF16, D, _p(tile_group), tiles, _p(row_dest),

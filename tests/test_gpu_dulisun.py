@@ -492,6 +492,34 @@ def test_greedy_generation_through_the_entry_point(models):
     assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
 
 
+def test_sampling_and_the_command_line(models):
+    """Sampling through the scheduler (temperature, top-p, top-k) runs and repeats under the same seed; the
+    command line generates the plain implementation's greedy tokens and describes the model."""
+    import subprocess
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d, reqs, _ = models["Q"]
+    eng = H.engine_for(d, "bfloat16", 16, 512)
+    params = SamplingParams(temperature=0.8, top_p=0.9, top_k=40, max_tokens=12, stop_token_ids=[], seed=7)
+    a = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
+    b = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
+    assert [r.tokens for r in a] == [r.tokens for r in b] and all(len(r.tokens) == 12 for r in a)
+    cfg, tensors = load_plain(d)
+    seq, want = list(reqs[1]), []
+    for _ in range(5):
+        t = int(np.argmax(pd.forward(cfg, tensors, seq)[-1]))
+        seq.append(t); want.append(t)
+    exe = os.path.join(H.ROOT, "bin", "aien-b200")
+    out = subprocess.run([exe, "generate", "--model-dir", d, "--dtype", "float32", "--prompt-ids", ",".join(map(str, reqs[1])),
+                          "--max-tokens", "5", "--temperature", "0", "--stop-token-ids", "", "--json"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert json.loads(out.stdout.strip().splitlines()[-1])["tokens"] == [want]
+    info = subprocess.run([exe, "info", "--model-dir", d], capture_output=True, text=True, timeout=600)
+    assert info.returncode == 0, info.stderr[-2000:]
+    rec = json.loads(info.stdout.strip().splitlines()[-1])
+    assert rec["architecture"] == "Dulisun" and rec["layers"] == 2 and rec["cache_groups"] == ["chunk", "chunk"]
+
+
 def test_trace_replay_from_the_command(models, tmp_path):
     d, reqs, want = models["Q"]
     toks = reqs[3]
