@@ -64,7 +64,7 @@ branch_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_pa
 // so a step of few rows still spreads a row's loads over many threads.  Parts are added in the order
 // of the plain kernel above; the sum of squares has a fixed order of its own.  Which of the two
 // kernels a row takes follows from H alone, never from the step.
-constexpr int BN_VECS = 4;
+constexpr int BN_VECS = 4;        // at most; a row of up to 512 / 1,024 vectors takes the kernel made for 1 / 2 (fewer registers, more CTAs an SM)
 
 __device__ __forceinline__ float4 f4_add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 
@@ -85,7 +85,7 @@ __device__ __forceinline__ void store_h4(__nv_bfloat16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = r;
 }
 
-template <typename TA, typename TB, typename TH>
+template <typename TA, typename TB, typename TH, int NV>
 __global__ void __launch_bounds__(512)
 branch_norm_add_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_parts, size_t a_stride,
                            const TB* __restrict__ b, int b_parts, size_t b_stride,
@@ -93,17 +93,17 @@ branch_norm_add_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, int 
     __shared__ float red[32];
     griddep_launch();
     const int nvec = H >> 2;
-    float4 wv[BN_VECS];
+    float4 wv[NV];
 #pragma unroll
-    for (int j = 0; j < BN_VECS; ++j) {                                   // the weights do not depend on the kernel ahead
+    for (int j = 0; j < NV; ++j) {                                   // the weights do not depend on the kernel ahead
         const int v = threadIdx.x + j * blockDim.x;
         wv[j] = v < nvec ? *reinterpret_cast<const float4*>(w + 4 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     griddep_wait();
     const size_t base = (size_t)blockIdx.x * H;
-    float4 y[BN_VECS], xv[BN_VECS];
+    float4 y[NV], xv[NV];
 #pragma unroll
-    for (int j = 0; j < BN_VECS; ++j) {
+    for (int j = 0; j < NV; ++j) {
         const int v = threadIdx.x + j * blockDim.x;
         y[j] = xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (v < nvec) {
@@ -114,11 +114,11 @@ branch_norm_add_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, int 
     }
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < BN_VECS; ++j) ss += y[j].x * y[j].x + y[j].y * y[j].y + y[j].z * y[j].z + y[j].w * y[j].w;
+    for (int j = 0; j < NV; ++j) ss += y[j].x * y[j].x + y[j].y * y[j].y + y[j].z * y[j].z + y[j].w * y[j].w;
     const float total = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(total / (float)H + eps);
 #pragma unroll
-    for (int j = 0; j < BN_VECS; ++j) {
+    for (int j = 0; j < NV; ++j) {
         const int v = threadIdx.x + j * blockDim.x;
         if (v < nvec) {
             const float4 r = make_float4(xv[j].x + y[j].x * scale * wv[j].x, xv[j].y + y[j].y * scale * wv[j].y,
@@ -169,9 +169,14 @@ AIEN_API int aien_branch_norm_add(float* x, const void* a, int a_dt, int a_parts
                              (a_stride & 3) == 0 && (b_stride & 3) == 0 &&
                              (a_dt == AIEN_DT_F32 || ((uintptr_t)a & 7) == 0) && (b == nullptr || b_dt == AIEN_DT_F32 || ((uintptr_t)b & 7) == 0);
         if (aligned) {
-            AIEN_DISPATCH_DTYPE(a_dt, TA, AIEN_DISPATCH_DTYPE(b_dt, TB, AIEN_DISPATCH_DTYPE(h_dt, TH,
-                (launch_chain(branch_norm_add_vec_kernel<TA, TB, TH>, dim3(T), dim3(threads), 0, stream,
-                              x, (const TA*)a, a_parts, a_stride, (const TB*)b, b_parts, b_stride, (const float*)w, eps, (TH*)h, H)))));
+#define BN_LAUNCH(NVV)                                                                                                          \
+            AIEN_DISPATCH_DTYPE(a_dt, TA, AIEN_DISPATCH_DTYPE(b_dt, TB, AIEN_DISPATCH_DTYPE(h_dt, TH,                               \
+                (launch_chain(branch_norm_add_vec_kernel<TA, TB, TH, NVV>, dim3(T), dim3(threads), 0, stream,                        \
+                              x, (const TA*)a, a_parts, a_stride, (const TB*)b, b_parts, b_stride, (const float*)w, eps, (TH*)h, H)))))
+            if (nvec <= threads) { BN_LAUNCH(1); }
+            else if (nvec <= 2 * threads) { BN_LAUNCH(2); }
+            else { BN_LAUNCH(4); }
+#undef BN_LAUNCH
             return launch_status();
         }
     }

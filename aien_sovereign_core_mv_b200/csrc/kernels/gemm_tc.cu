@@ -41,12 +41,20 @@ template <int AR, int BN> struct TcT {
     static constexpr int TMEM_COLS = BN <= 64 ? 64 : 128;
 };
 
-// Stores 32 consecutive accumulator columns of one row: r holds columns n0+c0 .. +31 of row `row`.
-// EPI 0: as they are; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns).
-template <int EPI, typename TC>
-__device__ __forceinline__ void tc_store_chunk(const uint32_t r[32], TC* __restrict__ out, long ldc, int row, int n0, int c0, int N) {
+__device__ __forceinline__ float tc_gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
+__device__ __forceinline__ float tc_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 
-                if (EPI == 0) {
+// Stores 32 consecutive accumulator columns of one row: r holds columns n0+c0 .. +31 of row `row`.
+// EPI 0: as they are; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns);
+// EPI 2 / 3: the gelu in its erf / tanh form of every value.
+template <int EPI, typename TC>
+__device__ __forceinline__ void tc_store_chunk(const uint32_t r_in[32], TC* __restrict__ out, long ldc, int row, int n0, int c0, int N) {
+                uint32_t r[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    r[j] = EPI == 2 ? __float_as_uint(tc_gelu_erf(__uint_as_float(r_in[j])))
+                                    : (EPI == 3 ? __float_as_uint(tc_gelu_tanh(__uint_as_float(r_in[j]))) : r_in[j]);
+                if (EPI != 1) {
                     TC* dst = out + (size_t)row * ldc + n0 + c0;
                     const int valid = N - (n0 + c0);
                     if (valid >= 32 && (((uintptr_t)dst & 15) == 0)) {
@@ -214,9 +222,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 //   row_dest != nullptr: row r of the result goes to row row_dest[r] of out (-1: nowhere) times
 //   row_scale[r]: the weighted outputs of routed experts, back in token order.
 // Columns of a tile beyond N belong to the next group's rows of W; they are computed and not stored.
-__device__ __forceinline__ float tc_gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
-__device__ __forceinline__ float tc_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
-
 template <int EPI, typename TC>
 __global__ void __launch_bounds__(192)
 gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -792,7 +797,8 @@ static int launch_tc(const void* A, long lda, const void* W, long ldw, void* out
 
 using namespace aien;
 
-// epilogue 0: out[M,N]; 1: out[M,N/2] = silu(gate)*up with gate/up rows of W interleaved in runs of 8.
+// epilogue 0: out[M,N]; 1: out[M,N/2] = silu(gate)*up with gate/up rows of W interleaved in runs of 8;
+// 2 / 3: out[M,N] = gelu (erf / tanh form) of the product, bfloat16.
 // splits > 1 (epilogue 0, float32 out): K is cut into ranges of whole 64-value blocks and out is
 // [ranges][M][ldc] partial products, part_stride elements apart; aien_gemm_tc_ranges says how many
 // ranges a given (K, splits) really makes.
@@ -818,6 +824,19 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
     if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + 95) / 96 > 65535) return AIEN_E_SHAPE;
+    if (epilogue == 2 || epilogue == 3) {          // gelu (erf / tanh form) of every value, bfloat16 out, K in one range
+        if (c_dt != AIEN_DT_BF16 || splits != 1) return AIEN_E_SHAPE;
+        const int plan = tc_plan(M, N, 1);
+        const int wide = plan == 256 ? tc_m256_cols(M, N, K, 1) : 0;
+        if (epilogue == 2) {
+            if (wide > 0) return launch_tc_persistent_m256<2, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (plan == 256) return launch_tc_persistent<256, 2, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, 1, 0, stream);
+            return launch_tc<2, __nv_bfloat16>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
+        }
+        if (wide > 0) return launch_tc_persistent_m256<3, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+        if (plan == 256) return launch_tc_persistent<256, 3, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, 1, 0, stream);
+        return launch_tc<3, __nv_bfloat16>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
+    }
     if (epilogue == 0 || epilogue == 1) {
         const int plan = tc_plan(M, N, aien_gemm_tc_ranges(K, splits));
 #define TCP_CASE(BNV, EPIV, T) return launch_tc_persistent<BNV, EPIV, T>(A, lda, W, ldw, out, ldc, M, N, K, splits, part_stride, stream)

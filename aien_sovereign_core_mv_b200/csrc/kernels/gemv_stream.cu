@@ -59,7 +59,7 @@ struct GsFuse {
     float* ssq_out;            // [gridDim.x][16]
 };
 
-// MT token tiles of 8; EPI 0 store / 1 swiglu / 2 residual; STAGES ring depth
+// MT token tiles of 8; EPI 0 store / 1 swiglu / 2 residual / 3, 4 gelu (erf, tanh form) then store; STAGES ring depth
 template <int MT, int EPI, typename TC, int STAGES>
 __global__ void __launch_bounds__(GS_THREADS, 1)
 gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -232,7 +232,14 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             ss[mt][i & 1] += xn * xn;
                         }
                     }
-                } else if (EPI == 0) {
+                } else if (EPI == 0 || EPI >= 3) {
+                    if (EPI == 3) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) sum[i] = 0.5f * sum[i] * (1.0f + erff(sum[i] * 0.7071067811865476f));
+                    } else if (EPI == 4) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) sum[i] = 0.5f * sum[i] * (1.0f + tanhf(0.7978845608028654f * (sum[i] + 0.044715f * sum[i] * sum[i] * sum[i])));
+                    }
                     if (r0 < N) {
                         if (t0 < M) o[(size_t)t0 * ldc + r0] = from_f<TC>(sum[0]);
                         if (t0 + 1 < M) o[(size_t)(t0 + 1) * ldc + r0] = from_f<TC>(sum[1]);
@@ -328,6 +335,8 @@ static int gemv_stream_dispatch(const void* a, long lda, const void* W, long ldw
         return AIEN_E_DTYPE;
     }
     if (epilogue == 2) { if (M <= 8) GS_CASE(1, 2, float); else GS_CASE(2, 2, float); }
+    if (epilogue == 3 && c_dt == AIEN_DT_BF16 && splits == 1) { if (M <= 8) GS_CASE(1, 3, __nv_bfloat16); else GS_CASE(2, 3, __nv_bfloat16); }
+    if (epilogue == 4 && c_dt == AIEN_DT_BF16 && splits == 1) { if (M <= 8) GS_CASE(1, 4, __nv_bfloat16); else GS_CASE(2, 4, __nv_bfloat16); }
 #undef GS_CASE
     return AIEN_E_SHAPE;
 }
@@ -337,7 +346,7 @@ static int gemv_stream_dispatch(const void* a, long lda, const void* W, long ldw
 // partial products are written as zeros.
 AIEN_API int aien_gemv_stream_bf16(const void* a, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
                                    int M, int N, int K, int epilogue, int splits, size_t part_stride, cudaStream_t stream) {
-    if (epilogue != 0 && epilogue != 1) return AIEN_E_SHAPE;
+    if (epilogue != 0 && epilogue != 1 && epilogue != 3 && epilogue != 4) return AIEN_E_SHAPE;    // 3 / 4: gelu (erf / tanh form), bfloat16 out
     GsFuse none = {};
     return gemv_stream_dispatch(a, lda, W, ldw, out, c_dt, ldc, M, N, K, epilogue, splits, part_stride, none, stream);
 }

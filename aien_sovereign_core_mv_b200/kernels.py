@@ -646,6 +646,7 @@ def gemv_splits(N: int, K_: int) -> int:
 def gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
     """out = a . w^T for up to 16 rows of a (bfloat16, float32 accumulation).  ``epilogue=1``:
     w holds gate|up rows interleaved in groups of 8 and out = silu(gate)*up with N/2 columns.
+    ``epilogue=3`` / ``4`` (the streamed kernel, bfloat16 out): the gelu in its erf / tanh form of every value.
     ``out`` of shape [P, M, N] float32 receives P partial products over P ranges of K."""
     _dev(a, w, out)
     M, K_ = a.shape
@@ -655,10 +656,16 @@ def gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0)
         assert epilogue == 0 and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape[1:]) == (M, N)
         splits, part_stride = out.shape[0], M * N
     else:
-        assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
+        assert w.shape[1] == K_ and out.shape == (M, N // 2 if epilogue == 1 else N)
+    assert epilogue in (0, 1) or gemv_takes_activation(K_)
     fn = lib().aien_gemv_stream_bf16 if (GEMV_IMPL == "stream" and K_ % 64 == 0) else lib().aien_gemv_bf16
     _check(fn(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(-2), M, N, K_,
               epilogue, splits, part_stride, _stream()), "gemv_bf16")
+
+
+def gemv_takes_activation(K_: int) -> bool:
+    """Whether the decode product over K_ columns has the gelu epilogues (the streamed kernel has, the direct one has not)."""
+    return GEMV_IMPL == "stream" and K_ % 64 == 0
 
 
 def gemv_stream_error() -> int:
@@ -676,7 +683,7 @@ def gemm_tc_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
     """out = a . w^T on the tcgen05 tensor cores (bfloat16 operands, float32 accumulation in
     tensor memory).  ``epilogue=1``: w holds gate|up rows interleaved in runs of 8 and
-    out = silu(gate)*up with N/2 columns."""
+    out = silu(gate)*up with N/2 columns.  ``epilogue=2`` / ``3`` (bfloat16 out): the gelu in its erf / tanh form."""
     _dev(a, w, out)
     M, K_ = a.shape
     N = w.shape[0]
@@ -686,7 +693,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
         assert out.shape[0] == gemm_tc_ranges(K_, out.shape[0])
         splits, part_stride = out.shape[0], M * N
     else:
-        assert w.shape[1] == K_ and out.shape == (M, N if epilogue == 0 else N // 2)
+        assert w.shape[1] == K_ and out.shape == (M, N // 2 if epilogue == 1 else N)
     _check(lib().aien_gemm_tc(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), dt(out), out.stride(-2), M, N, K_,
                               epilogue, splits, part_stride, _stream()), "gemm_tc")
 

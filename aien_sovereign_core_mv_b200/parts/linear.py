@@ -19,8 +19,12 @@ _FORCE = os.environ.get("AIEN_B200_GEMM", "").strip().lower()
 
 
 def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None, may_defer_sum: bool = False) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, may_defer_sum: bool = False, act: Optional[int] = None) -> torch.Tensor:
     """a [M, K] (row stride free), w [N, K] -> [M, N] taken from the step workspace.
+
+    ``act`` (0: the gelu in its erf form, 1: in its tanh form): the activation of every value of the
+    product, in the product's epilogue where the kernel has one (bfloat16 results of the streamed
+    decode product and of the tensor-core kernel), else by a kernel of its own behind it.
 
     ``may_defer_sum``: the caller's consumer can add partial products, so the decode kernel may
     cut K across CTAs and return float32 partials [P, M, N] instead (the norm kernel, the q/k
@@ -45,12 +49,17 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
     if out is None:
         out = ctx.workspace.take((M, N), out_dtype or a.dtype)
     choice = _FORCE or _choose(a, w, out, M)
+    fused = act is not None and out.dtype == torch.bfloat16 and out.is_contiguous()
     if choice == "gemv":
-        K.gemv(a, w, out)
+        fused = fused and K.gemv_takes_activation(a.shape[1])
+        K.gemv(a, w, out, epilogue=3 + act if fused else 0)
     elif choice == "tc":
-        K.gemm_tc(a, w, out)
+        K.gemm_tc(a, w, out, epilogue=2 + act if fused else 0)
     else:
+        fused = False
         K.gemm_simple(a, w, out)
+    if act is not None and not fused:
+        K.act_rows(out, act)
     return out
 
 

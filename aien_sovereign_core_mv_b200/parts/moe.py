@@ -90,7 +90,6 @@ class RoutedExperts(FeedForward):
         parts = K.moe_experts(ctx, h, self.w_up, self.w_down, ids, wts, top, self.act)
         shared = None
         if self.shared_ff:
-            a = linear(ctx, h, self.w_shared_up)
-            K.act_rows(a, self.shared_act)
+            a = linear(ctx, h, self.w_shared_up, act=self.shared_act)          # the activation in the product's epilogue
             shared = linear(ctx, a, self.w_shared_down, out_dtype=torch.float32, may_defer_sum=True)
         return parts, shared

@@ -351,6 +351,22 @@ def test_routed_feed_forward_part(dtype, T, shared, D, F, E, top):
     H.assert_close(got.cpu().numpy(), want, 2e-5 if dtype == torch.float32 else 2e-2, "routed feed-forward")
 
 
+@pytest.mark.parametrize("M,N,K", [(3, 192, 256), (12, 1536, 512), (70, 200, 128), (600, 1536, 2048), (2048, 1536, 2048), (2048, 768, 1024)])
+@pytest.mark.parametrize("act", [0, 1])
+def test_products_with_the_activation_in_their_epilogue(M, N, K, act):
+    """The streamed decode product (few rows) and every form of the tensor-core product (tiles, persistent,
+    256-row tiles) with the gelu of both forms in the epilogue, against a float64 product and activation."""
+    from aien_sovereign_core_mv_b200.parts.linear import linear
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    ctx = make_ctx(torch.bfloat16, list(range(M)), [0] * M, [0, M], [M])
+    y = linear(ctx, a.cuda(), w.cuda(), act=act)
+    z = a.double().numpy() @ w.double().numpy().T
+    want = pd.gelu_erf(z) if act == 0 else pd.gelu_tanh(z)
+    H.assert_close(y.float().cpu().numpy(), want, 8e-3, "product with activation")
+
+
 # ------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype,tol", DTYPES)
 @pytest.mark.parametrize("which", list(CONFIGS))
