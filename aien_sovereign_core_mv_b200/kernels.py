@@ -1001,6 +1001,18 @@ def decode_splits(max_ctx: int, chunk: int) -> int:
     return min(splits, (chunk + DECODE_CHUNK - 1) // DECODE_CHUNK + 1) if chunk > 0 else splits
 
 
+def decode_masked_takes(num_q_heads: int, num_kv_heads: int, head_dim: int, splits: int) -> bool:
+    """Whether the split-key kernel's shared memory (a block of keys and values, scores, and the merge's
+    scratch, which grows with the number of blocks) stays within what a CTA can have; else the plain kernel runs."""
+    G = num_q_heads // num_kv_heads
+    nh = 8 * ((G + 7) // 8)
+    loop = (DECODE_CHUNK * nh + 2 * nh) * 4 + nh * DECODE_CHUNK * 2
+    r4 = lambda n: (n + 3) & ~3
+    merge = (r4(G) + r4(splits * G) + max(r4(splits * G), 8 * head_dim)) * 4
+    kv = DECODE_CHUNK * (head_dim * 2 + 16) * 2
+    return ((max(loop, merge) + 127) & ~127) + kv <= 200 * 1024 - 1024
+
+
 def chunk_attention_workspace_bytes(lim, num_heads: int, value_dim: int, chunk: int) -> int:
     """Scratch of attention under a chunk mask for the largest step: the partial results of the split-key kernel."""
     return lim.max_seqs * num_heads * decode_splits(lim.max_context, chunk) * (value_dim + 2) * 4 + 4096
@@ -1026,7 +1038,7 @@ def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
                                ctx.positions, out, part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
                                splits, token_list=tokens, num_tokens=n, impl="direct", chunk=chunk, sinks=sinks)
 
-    if ctx.decode_only and split_key:
+    if ctx.decode_only and split_key and decode_masked_takes(num_q_heads, num_kv_heads, head_dim, decode_splits(ctx.max_ctx_len, chunk)):
         single_tokens(None, q.shape[0])
         return
     if (not ctx.decode_only and _FORCE_ATTN != "generic" and ctx.prefill_tiles is not None and value_dim == head_dim
@@ -1039,7 +1051,7 @@ def chunk_sink_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: t
                                     out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
                                     chunk=chunk, sinks=sinks)
         tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
-        if nd > 0 and split_key:
+        if nd > 0 and split_key and decode_masked_takes(num_q_heads, num_kv_heads, head_dim, decode_splits(ctx.max_ctx_len, chunk)):
             single_tokens(tokens, nd)
         elif nd > 0:
             paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,

@@ -69,7 +69,7 @@ def _attention_parts(i: int, mixer: Mapping[str, Any], width: int, eps: float):
     where = f"layers[{i}].mixer"
     dim = _need(mixer, "dim", where, int)
     rot = mixer.get("rot")
-    if rot:
+    if rot and rot.get("dims"):
         position = PartSpec("rotary", {"head_dim": dim, "theta": _need(rot, "base", where + ".rot", float),
                                        "rotary_dim": _need(rot, "dims", where + ".rot", int), "pairing": "interleaved",
                                        "theta_as_float32": False})

@@ -57,7 +57,7 @@ def rotate_interleaved(v, positions, base, dims):
 # ------------------------------------------------------------------ attention
 def chunk_sink_attention(q, k, v, q_pos, k_pos, scale, chunk, sink):
     """q [Tq, H, d], k [Tk, G, d], v [Tk, G, dv]; query at position i sees the key at position j
-    iff j <= i and floor(i / chunk) == floor(j / chunk).  Per head the softmax denominator also
+    iff j <= i and floor(i / chunk) == floor(j / chunk) (``chunk`` None or 0: every j <= i).  Per head the softmax denominator also
     holds exp(sink[h]), which has no key and no value.  Returns [Tq, H, dv]."""
     Tq, H, _ = q.shape
     G = k.shape[1]
@@ -65,7 +65,7 @@ def chunk_sink_attention(q, k, v, q_pos, k_pos, scale, chunk, sink):
     out = np.zeros((Tq, H, v.shape[2]))
     for t in range(Tq):
         i = int(q_pos[t])
-        vis = [n for n, j in enumerate(k_pos) if j <= i and (int(j) // chunk) == (i // chunk)]
+        vis = [n for n, j in enumerate(k_pos) if j <= i and (not chunk or (int(j) // chunk) == (i // chunk))]
         for h in range(H):
             g = h // rep
             s = np.array([float(np.dot(q[t, h], k[n, g])) * scale for n in vis] + [float(sink[h])])
@@ -86,7 +86,7 @@ def attention_mixer(h, positions, W, mc, eps, past=None):
     q = (h @ W["q"].T.astype(np.float64)).reshape(T, H, d)
     kp = (h @ W["k"].T.astype(np.float64)).reshape(T, G, d)
     v = kp[:, :, :dv].copy()                                    # the values are the keys as projected
-    rot = mc["rot"]
+    rot = mc.get("rot") or {"base": 1.0, "dims": 0}
     q = unit_rms(rotate_interleaved(q, positions, rot["base"], rot["dims"]), eps)
     k = unit_rms(rotate_interleaved(kp, positions, rot["base"], rot["dims"]), eps)
     pos = np.asarray(positions)
@@ -96,7 +96,7 @@ def attention_mixer(h, positions, W, mc, eps, past=None):
         kpos = np.concatenate([past[2], pos])
     else:
         kpos = pos
-    a = chunk_sink_attention(q, k, v, pos, kpos, mc["scale"], mc["mask"]["size"], W["sink"].astype(np.float64))
+    a = chunk_sink_attention(q, k, v, pos, kpos, mc["scale"], (mc.get("mask") or {}).get("size"), W["sink"].astype(np.float64))
     y = a.reshape(T, H * dv) @ W["o"].T.astype(np.float64)
     return y, (k, v, kpos)
 
