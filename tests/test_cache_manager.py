@@ -103,6 +103,44 @@ def test_window_gives_pages_back():
     assert cm2.num_tokens(1) == 105 and cm2.check() == ""
 
 
+def test_chunk_groups_hold_only_the_chunk_of_the_next_token():
+    """Chunks of 6 positions on pages of 4: before a step's allocations the pages that lie wholly before the
+    chunk of the request's next token go back; a portion that starts inside a chunk keeps that chunk's pages,
+    whatever chunks the portion itself reaches."""
+    Chunk = host.GroupKind.Chunk
+    cm = host.CacheManager(4, [host.GroupSpec(Full, 0, 32), host.GroupSpec(Chunk, 6, 8)], 2)
+    cm.add_request(1)
+    for n in range(1, 41):
+        cm.append([(1, 1)])
+        pos = n - 1                                          # the token this step brought
+        start = (pos // 6) * 6
+        for j in range(start, pos + 1):                      # every key of its chunk has its slot
+            assert cm.slot_of(1, 1, j) >= 0, (pos, j)
+        tbl = cm.table(1, 1)
+        assert all(p == -1 for p in tbl[:start // 4])        # everything wholly before the chunk is gone
+        assert sum(1 for p in tbl if p >= 0) <= 3
+    assert cm.metrics()["window_releases"] >= 8 and cm.check() == ""
+    # a portion from position 40 (chunk 36..41) over several chunks: needs its own pages plus the held one
+    cm.append([(1, 17)])
+    assert cm.slot_of(1, 1, 36) >= 0 and cm.slot_of(1, 1, 56) >= 0 and cm.slot_of(1, 1, 35) == -1
+    # the next step starts at 57 (chunk 54..59): pages before position 54 // 4 * 4 = 52 go back
+    cm.append([(1, 1)])
+    assert cm.slot_of(1, 1, 54) >= 0 and cm.slot_of(1, 1, 51) == -1 and cm.check() == ""
+    # a request far longer than the group's pool fits; one whose portion needs more pages than the pool is refused whole
+    with pytest.raises(RuntimeError, match=host.EXHAUSTED_PREFIX):
+        cm.append([(1, 40)])
+    assert cm.num_tokens(1) == 58 and cm.check() == ""
+    # truncating to a position whose chunk's pages were given back is refused; inside the held chunk it works
+    with pytest.raises(ValueError):
+        cm.truncate(1, 40)
+    cm.truncate(1, 56)
+    assert cm.num_tokens(1) == 56 and cm.check() == ""
+    cm.free_request(1)
+    assert cm.free_count(1) == 8 and cm.check() == ""
+    with pytest.raises(ValueError):
+        host.CacheManager(4, [host.GroupSpec(Chunk, 0, 8)], 2)
+
+
 def test_fork_shares_and_copies_on_write():
     cm = manager(page=4, pages=16, state=True)
     cm.add_request(1)

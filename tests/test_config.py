@@ -113,3 +113,41 @@ def test_run_list_validation():
     for bad in [(RunEntry(0, 0), RunEntry(1, 0)), (RunEntry(0, 1, False),), (RunEntry(5, 0),)]:
         with pytest.raises(ValueError):
             dataclasses.replace(spec, run_list=bad).validate()
+
+
+# ------------------------------------------------------------------ Dulisun: layers listed one by one
+def _dulisun_config():
+    attn = lambda heads, kv, dim, chunk: {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "rot": {"base": 5000.0, "dims": dim // 2},
+                                          "mask": {"size": chunk}, "scale": 0.2}
+    moe = {"kind": "moe", "expert": {"ff": 24}, "shared": {"ff": 40},
+           "router": {"experts": 6, "top": 2, "groups": {"count": 3, "keep": 2}}}
+    return {"architecture": "Dulisun", "vocab": 97, "width": 48, "norm": {"eps": 2e-6}, "layers": [
+        {"type": "attention", "mixer": attn(4, 2, 16, 12), "mlp": moe},
+        {"type": "attention", "mixer": attn(2, 1, 32, 12), "mlp": None},
+        {"type": "attention", "mixer": attn(4, 4, 8, 20), "mlp": dict(moe, shared=None)}]}
+
+
+def test_dulisun_spec_catalog_and_cache_groups():
+    from aien_sovereign_core_mv_b200 import ConfigError, model_spec_for
+    from aien_sovereign_core_mv_b200.models import Decoder
+    cfg, spec = model_spec_for(_dulisun_config())
+    assert spec.architecture == "Dulisun" and spec.hidden_size == 48 and spec.vocab_size == 97 and len(spec.layers) == 3
+    assert [l.block for l in spec.layers] == ["branchnorm", "branchnorm_mixer", "branchnorm"]
+    assert spec.layers[0].mixer.params["chunk"] == 12 and spec.layers[0].mixer.params["unit_eps"] == 2e-6
+    assert spec.layers[0].feed_forward.params["group_keep"] == 2 and spec.layers[2].feed_forward.params["shared_ff"] == 0
+    model = Decoder(spec)
+    cat = model.catalog()
+    assert cat["embed"][0] == (97, 48) and cat["embed.norm"][0] == (48,) and cat["final.norm"][0] == (48,)
+    assert cat["l0.mix.q"][0] == (64, 48) and cat["l0.mix.k"][0] == (32, 48) and cat["l0.mix.o"][0] == (48, 64) and cat["l0.mix.sink"][0] == (4,)
+    assert cat["l0.mlp.router"][0] == (6, 48) and cat["l0.mlp.e5.up"][0] == (24, 48) and cat["l0.mlp.e5.down"][0] == (48, 24)
+    assert cat["l0.mlp.shared.up"][0] == (40, 48) and "l2.mlp.shared.up" not in cat
+    assert "l1.norm2" not in cat and "l1.norm1" in cat and not any(n.startswith("l1.mlp") for n in cat)
+    assert not any("mix.v" in n for n in cat)                              # the values are the keys: no value projection
+    # layers 0 and 1 keep chunks of 12 but planes of different shapes; layer 2 keeps chunks of 20
+    assert [n.kind for n in model.group_needs] == ["chunk", "chunk", "chunk"] and [n.window for n in model.group_needs] == [12, 12, 20]
+    bad = _dulisun_config(); bad["layers"][0]["mlp"]["router"]["top"] = 5     # 2 groups of 2 experts stay eligible
+    with pytest.raises(ValueError, match="top 5"):
+        Decoder(model_spec_for(bad)[1])
+    bad = _dulisun_config(); del bad["vocab"]
+    with pytest.raises(ConfigError, match="vocab"):
+        model_spec_for(bad)
