@@ -1,18 +1,21 @@
-// Routed feed-forward: the router's choice and the plain expert products.
+// Routed feed-forward: the router's choice, the rows sorted by expert for the grouped tensor-core
+// products (gemm_tc.cu), the experts' products of a few tokens, and the plain expert products.
 //
 //   route        scores s = softmax(z) over all E experts (float32); experts lie in `groups` equal
 //                groups of neighbours, a group scores its best expert, only the `keep` best groups
 //                stay eligible; the `top` best eligible experts are taken, weight = their score
 //                (divided by the sum of the taken scores when `renorm` is set).  Ties go to the lower
-//                index.  One warp per token.
+//                index.  One warp per token.  On request it also counts the choices per expert.
+//   plan_rows, place_rows   every expert's (token, choice) pairs in a run of rows of their own (see below)
+//   expert_rows_bf16        up and down products of a few tokens, bfloat16, a warp per four output rows
 //   expert_up    act[t, c, :] = f(W_up[e(t,c)] h[t])             c < top, f = gelu (erf or tanh form)
 //   expert_down  part[c][t, :] = weight(t,c) * W_down[e(t,c)] act[t, c, :]   float32 parts, one per choice,
 //                which the consumer (the norm that takes the branch) adds in index order
 //   act_rows     f applied in place to [T, F] rows (the shared expert's hidden layer)
 //
-// The products here are one warp per output value with the reduction in a fixed lane order, so a
-// token's result depends on its own row alone; they serve the 32-bit engine and small steps, and
-// are what the grouped tensor-core products are held to.
+// expert_up / expert_down are one warp per output value with the reduction in a fixed lane order, so a
+// token's result depends on its own row alone; they serve the 32-bit engine and sizes the others do not
+// take, and are what the faster products are held to.
 #include "common.cuh"
 #include <math.h>
 
@@ -28,7 +31,7 @@ constexpr int ROUTE_MAX_EXPERTS = 1024;
 
 __global__ void __launch_bounds__(32)
 moe_route_kernel(const float* __restrict__ z, int E, int groups, int keep, int top, int renorm,
-                 int* __restrict__ ids, float* __restrict__ wts) {
+                 int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ expert_count) {
     __shared__ float s[ROUTE_MAX_EXPERTS];
     __shared__ float gs[ROUTE_MAX_EXPERTS];
     griddep_launch();
@@ -80,6 +83,7 @@ moe_route_kernel(const float* __restrict__ z, int E, int groups, int keep, int t
             ids[(size_t)t * top + r] = bi;
             wts[(size_t)t * top + r] = bv;
             s[bi] = -2.0f;                                 // taken
+            if (expert_count != nullptr) atomicAdd(expert_count + bi, 1);     // for the plan of the grouped products
         }
         wsum += bv;
         __syncwarp();
@@ -130,81 +134,80 @@ moe_expert_down_kernel(const TA* __restrict__ act, const TW* __restrict__ w_down
 }
 
 // ---------------------------------------------------------------- rows sorted by expert, for the grouped product
-// One CTA.  Pair p = t * top + c chose expert ids[p].  Every expert's pairs get a run of rows that
-// starts at a multiple of 128 (the row tile of the grouped tensor-core product); the runs follow one
-// another in expert order.  Out: tile_group[i] = expert of row tile i (-1 beyond the last run);
-// row_pair[r] = the pair in row r (-1: padding); row_dest[r] = c * T + t, the row of the [top, T, D]
-// parts that the pair's output belongs to (-1: padding); row_scale[r] = the pair's weight.
-// Which row of its run a pair gets depends on the order the threads arrive in; no result depends on
-// it, since a row of a product depends on that row alone.
+// Pair p = t * top + c chose expert ids[p].  Every expert's pairs get a run of rows that starts at a multiple of 128
+// (the row tile of the grouped tensor-core product); the runs follow one another in expert order.
+//   tile_group[i] = expert of row tile i (-1 beyond the last run, whose rows are not written at all);
+//   row_dest[r] = c * T + t, the row of the [top, T, D] parts that the pair in row r belongs to (-1: padding);
+//   row_scale[r] = the pair's weight;  a_sorted[r, :] = the pair's token's row of h.
+// Which row of its run a pair gets depends on the order the threads arrive in; no result depends on it, since a row
+// of a product depends on that row alone.
 constexpr int SORT_THREADS = 1024;
 
+// Two launches.  The router's choice has counted the pairs of every expert (expert_count).  moe_plan_rows (one CTA): the first row of every expert's run, a cursor
+// into it, the experts of the row tiles, -1 as the destination of the padding rows; the counts are zeroed for the
+// next step.  moe_place_rows (64 threads a pair): the pair takes the next row of its expert's run and its token's
+// row of h is copied there, with the pair's destination and weight.  Padding rows of a_sorted are left as they are:
+// a row of a product depends on that row alone, and their results are never stored.
 __global__ void __launch_bounds__(SORT_THREADS)
-moe_sort_pairs_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int P, int T, int top, int E, int max_tiles,
-                      int* __restrict__ tile_group, int* __restrict__ row_pair, int* __restrict__ row_dest,
-                      float* __restrict__ row_scale) {
+moe_plan_rows_kernel(int* __restrict__ expert_count, int E, int max_tiles, int* __restrict__ cursor, int* __restrict__ tile_group,
+                     int* __restrict__ row_dest) {
     __shared__ int count[ROUTE_MAX_EXPERTS];
-    __shared__ int start[ROUTE_MAX_EXPERTS];      // first row of the expert's run
-    __shared__ int cursor[ROUTE_MAX_EXPERTS];     // next free row of the run
+    __shared__ int start[ROUTE_MAX_EXPERTS];
     __shared__ int used_rows;
     griddep_launch();
     griddep_wait();
     const int tid = threadIdx.x;
-    for (int e = tid; e < E; e += SORT_THREADS) count[e] = 0;
-    __syncthreads();
-    for (int p = tid; p < P; p += SORT_THREADS) atomicAdd(&count[__ldcg(ids + p)], 1);
+    for (int e = tid; e < E; e += SORT_THREADS) { count[e] = __ldcg(expert_count + e); expert_count[e] = 0; }
     __syncthreads();
     if (tid == 0) {
         int row = 0;
         for (int e = 0; e < E; ++e) {
-            start[e] = cursor[e] = row;
+            start[e] = row;
             row += (count[e] + 127) & ~127;
         }
         used_rows = row;
     }
     __syncthreads();
-    // tiles of a run belong to its expert; tiles beyond the last run are empty, and their rows stay unwritten
-    // (the gather and the products look at tile_group first)
+    for (int e = tid; e < E; e += SORT_THREADS) cursor[e] = start[e];
     for (int i = (used_rows >> 7) + tid; i < max_tiles; i += SORT_THREADS) tile_group[i] = -1;
     for (int e = tid; e < E; e += SORT_THREADS) {
         const int first = start[e] >> 7, n = (count[e] + 127) >> 7;
         for (int i = 0; i < n; ++i) tile_group[first + i] = e;
     }
-    // the padding rows at the end of every run
     for (int e = tid >> 7; e < E; e += SORT_THREADS >> 7) {
         const int r = start[e] + count[e] + (tid & 127);
-        if (r < start[e] + ((count[e] + 127) & ~127)) { row_pair[r] = -1; row_dest[r] = -1; row_scale[r] = 0.f; }
-    }
-    for (int p = tid; p < P; p += SORT_THREADS) {
-        const int e = __ldcg(ids + p);
-        const int r = atomicAdd(&cursor[e], 1);
-        const int t = p / top, c = p - t * top;
-        row_pair[r] = p;
-        row_dest[r] = c * T + t;
-        row_scale[r] = __ldcg(wts + p);
+        if (r < start[e] + ((count[e] + 127) & ~127)) row_dest[r] = -1;
     }
 }
 
-// a_sorted[r, :] = h[row_pair[r] / top, :] (zeros in padding rows; rows of empty tiles are left alone); bfloat16,
-// 16-byte vectors, D % 8 == 0.  Four rows a CTA, 64 threads a row: the row's pair is looked up once and up to four
-// vectors of a thread are in flight together.
 __global__ void __launch_bounds__(256)
-moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, long h_stride, const int* __restrict__ row_pair,
-                       const int* __restrict__ tile_group, int top, __nv_bfloat16* __restrict__ a_sorted, int D, int rows) {
+moe_place_rows_kernel(const __nv_bfloat16* __restrict__ h, long h_stride, const int* __restrict__ ids, const float* __restrict__ wts,
+                      int* __restrict__ cursor, int P, int T, int top, __nv_bfloat16* __restrict__ a_sorted, int D,
+                      int* __restrict__ row_dest, float* __restrict__ row_scale) {
+    __shared__ int rows[4];
     griddep_launch();
     griddep_wait();
-    const int r = blockIdx.x * 4 + (threadIdx.x >> 6), lane = threadIdx.x & 63;
-    if (r >= rows || __ldcg(tile_group + (r >> 7)) < 0) return;
-    const int p = __ldcg(row_pair + r);
+    const int sub = threadIdx.x >> 6, lane = threadIdx.x & 63;
+    const int p = blockIdx.x * 4 + sub;
+    if (p < P && lane == 0) {
+        const int r = atomicAdd(cursor + __ldcg(ids + p), 1);
+        const int t = p / top, c = p - t * top;
+        row_dest[r] = c * T + t;
+        row_scale[r] = __ldcg(wts + p);
+        rows[sub] = r;
+    }
+    __syncthreads();
+    if (p >= P) return;
+    const int r = rows[sub];
     const int vec = D >> 3;
-    const uint4* src = p >= 0 ? reinterpret_cast<const uint4*>(h + (size_t)(p / top) * h_stride) : nullptr;
+    const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(p / top) * h_stride);
     uint4* dst = reinterpret_cast<uint4*>(a_sorted + (size_t)r * D);
     for (int v0 = lane; v0 < vec; v0 += 256) {
         uint4 val[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int v = v0 + 64 * j;
-            val[j] = (src != nullptr && v < vec) ? __ldcg(src + v) : make_uint4(0u, 0u, 0u, 0u);
+            val[j] = v < vec ? __ldcg(src + v) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -290,12 +293,14 @@ __global__ void act_rows_kernel(T* __restrict__ a, size_t n, int act_kind) {
 
 using namespace aien;
 
+// expert_count (may be null): E ints that hold zero on entry; every choice adds one to its expert's
+// (aien_moe_plan_rows reads them and leaves zeros behind).
 AIEN_API int aien_moe_route(const float* z, int T, int E, int groups, int keep, int top, int renorm, int* ids, float* wts,
-                            cudaStream_t stream) {
+                            int* expert_count, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || E > ROUTE_MAX_EXPERTS || groups <= 0 || E % groups != 0 || keep <= 0 || keep > groups || top <= 0 ||
         top > keep * (E / groups)) return AIEN_E_SHAPE;
-    launch_chain(moe_route_kernel, dim3(T), dim3(32), 0, stream, z, E, groups, keep, top, renorm, ids, wts);
+    launch_chain(moe_route_kernel, dim3(T), dim3(32), 0, stream, z, E, groups, keep, top, renorm, ids, wts, expert_count);
     return launch_status();
 }
 
@@ -323,24 +328,21 @@ AIEN_API int aien_moe_expert_down(const void* act, int act_dt, const void* w_dow
     return launch_status();
 }
 
-// Rows for the grouped product; the arrays hold max_tiles (tile_group) and max_tiles * 128 entries.
-AIEN_API int aien_moe_sort_pairs(const int* ids, const float* wts, int T, int top, int E, int max_tiles, int* tile_group,
-                                 int* row_pair, int* row_dest, float* row_scale, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    const long P = (long)T * top;
-    if (E <= 0 || E > ROUTE_MAX_EXPERTS || top <= 0 || P > 2147483647L / 2 || (long)max_tiles * 128 < P + (long)E * 127) return AIEN_E_SHAPE;
-    launch_chain(moe_sort_pairs_kernel, dim3(1), dim3(SORT_THREADS), 0, stream, ids, wts, (int)P, T, top, E, max_tiles,
-                 tile_group, row_pair, row_dest, row_scale);
+// expert_count: what aien_moe_route counted (left zero); cursor: E ints of scratch; tile_group: max_tiles; row_dest: max_tiles * 128.
+AIEN_API int aien_moe_plan_rows(int* expert_count, int E, int max_tiles, int* cursor, int* tile_group, int* row_dest, cudaStream_t stream) {
+    if (E <= 0 || E > ROUTE_MAX_EXPERTS || max_tiles <= 0) return AIEN_E_SHAPE;
+    launch_chain(moe_plan_rows_kernel, dim3(1), dim3(SORT_THREADS), 0, stream, expert_count, E, max_tiles, cursor, tile_group, row_dest);
     return launch_status();
 }
 
-AIEN_API int aien_moe_gather_rows(const void* h, long h_stride, const int* row_pair, const int* tile_group, int top, void* a_sorted,
-                                  int D, int rows, cudaStream_t stream) {
-    if (rows <= 0) return 0;
+AIEN_API int aien_moe_place_rows(const void* h, long h_stride, const int* ids, const float* wts, int* cursor, int T, int top,
+                                 void* a_sorted, int D, int* row_dest, float* row_scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const long P = (long)T * top;
+    if (top <= 0 || P > 2147483647L / 2) return AIEN_E_SHAPE;
     if (D <= 0 || (D & 7) || (h_stride & 7) || ((uintptr_t)h & 15) || ((uintptr_t)a_sorted & 15)) return AIEN_E_ALIGN;
-    const int blocks = (rows + 3) / 4;
-    launch_chain(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)h, h_stride, row_pair, tile_group, top,
-                 (__nv_bfloat16*)a_sorted, D, rows);
+    launch_chain(moe_place_rows_kernel, dim3((unsigned)((P + 3) / 4)), dim3(256), 0, stream, (const __nv_bfloat16*)h, h_stride, ids, wts,
+                 cursor, (int)P, T, top, (__nv_bfloat16*)a_sorted, D, row_dest, row_scale);
     return launch_status();
 }
 

@@ -121,12 +121,12 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_branch_norm_add": [P, P, I, I, c_size_t, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
         "aien_stream_norm_inplace": [P, P, I, F, P, I, I, I, P],
         "aien_qk_rope_pairs_unit_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, I, I, F, P, P, I, P, P, P, I, I, I, P],
-        "aien_moe_route": [P, I, I, I, I, I, I, P, P, P],
+        "aien_moe_route": [P, I, I, I, I, I, I, P, P, P, P],
         "aien_moe_expert_up": [P, I, L, P, I, P, P, I, I, I, I, I, I, P],
         "aien_moe_expert_down": [P, I, P, I, P, P, P, I, I, I, I, P],
         "aien_act_rows": [P, I, c_size_t, I, P],
-        "aien_moe_sort_pairs": [P, P, I, I, I, I, P, P, P, P, P],
-        "aien_moe_gather_rows": [P, L, P, P, I, P, I, I, P],
+        "aien_moe_plan_rows": [P, I, I, P, P, P, P],
+        "aien_moe_place_rows": [P, L, P, P, P, I, I, P, I, P, P, P],
         "aien_moe_expert_rows_bf16": [I, P, L, P, P, P, P, I, I, I, I, I, P],
         "aien_gemm_tc_grouped": [P, L, P, L, I, P, I, L, P, I, P, P, I, I, I, P],
         "aien_argmax_rows": [P, I, I, P, P],
@@ -434,16 +434,19 @@ def qk_rope_pairs_unit_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: O
 ACT_KINDS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1}
 
 
-def moe_route(z: torch.Tensor, groups: int, keep: int, top: int, renorm: bool, ids: torch.Tensor, wts: torch.Tensor) -> None:
+def moe_route(z: torch.Tensor, groups: int, keep: int, top: int, renorm: bool, ids: torch.Tensor, wts: torch.Tensor,
+              expert_count: Optional[torch.Tensor] = None) -> None:
     """From router logits z [T,E] (float32): softmax scores, the ``keep`` best of ``groups`` equal groups of
     neighbouring experts (a group scores its best expert), the ``top`` best experts of those; ids int32
-    [T,top], wts float32 [T,top] = their scores (``renorm``: divided by their sum)."""
-    _dev(z, ids, wts)
+    [T,top], wts float32 [T,top] = their scores (``renorm``: divided by their sum).  ``expert_count`` (int32 [E],
+    zero on entry): every choice adds one to its expert's count, for the grouped products' plan, which zeroes it again."""
+    _dev(z, ids, wts, expert_count)
+    assert expert_count is None or (expert_count.dtype == torch.int32 and expert_count.is_contiguous() and expert_count.numel() >= z.shape[1])
     T, E = z.shape
     assert z.dtype == torch.float32 and z.is_contiguous() and ids.dtype == torch.int32 and wts.dtype == torch.float32
     assert ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top and wts.numel() >= T * top
-    _check(lib().aien_moe_route(_p(z), T, E, int(groups), int(keep), int(top), 1 if renorm else 0, _p(ids), _p(wts), _stream()),
-           "moe_route")
+    _check(lib().aien_moe_route(_p(z), T, E, int(groups), int(keep), int(top), 1 if renorm else 0, _p(ids), _p(wts), _p(expert_count),
+                                _stream()), "moe_route")
 
 
 def moe_expert_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: torch.Tensor, top: int, act_kind: int) -> None:
@@ -479,7 +482,7 @@ def moe_workspace_bytes(lim, num_experts: int, top: int, hidden: int, expert_ff:
     """Scratch of the grouped expert products for the largest step: the rows sorted by expert (inputs
     and hidden activations, bfloat16) and their maps."""
     tiles = _moe_tiles(lim.max_tokens * top, num_experts)
-    return tiles * 128 * ((hidden + expert_ff) * 2 + 12) + tiles * 4 + 8192
+    return tiles * 128 * ((hidden + expert_ff) * 2 + 8) + tiles * 4 + num_experts * 4 + 8192
 
 
 _MOE_IMPL = __import__("os").environ.get("AIEN_B200_MOE", "").strip().lower()      # "plain" pins the plain kernels
@@ -492,13 +495,18 @@ def moe_grouped_supports(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tens
             and w_up.data_ptr() % 16 == 0 and w_down.data_ptr() % 16 == 0)
 
 
+def moe_takes_grouped(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """Whether moe_experts runs this step on the grouped tensor-core products (the router then counts its choices per expert)."""
+    return _MOE_IMPL != "plain" and h.shape[0] > MOE_ROWS_MAX_TOKENS and moe_grouped_supports(h, w_up, w_down)
+
+
 def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor,
-                top: int, act_kind: int) -> torch.Tensor:
+                top: int, act_kind: int, expert_count: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Returns parts [top, T, D] with parts[c, t] = wts[t,c] * w_down[e] f(w_up[e] h[t]), e = ids[t,c]: the chosen
     experts of every token, weighted, one part per choice (float32; bfloat16 from the grouped products, whose
-    consumer adds them in float32).
+    consumer adds them in float32).  ``expert_count``: what moe_route counted; the grouped products need it.
     bfloat16: a few tokens stream their experts' rows (one warp per output value, 16-byte loads); larger
-    steps sort the (token, choice) pairs by expert and run two grouped tcgen05 products, the activation in
+    steps place the (token, choice) pairs in rows sorted by expert and run two grouped tcgen05 products, the activation in
     the first one's epilogue, the weights and the way back to token order in the second's.  float32, and
     sizes those kernels do not take: the plain products."""
     T, D = h.shape
@@ -506,6 +514,8 @@ def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, 
     ws = ctx.workspace
     ok = _MOE_IMPL != "plain" and moe_grouped_supports(h, w_up, w_down)
     grouped = ok and T > MOE_ROWS_MAX_TOKENS
+    if grouped and expert_count is None:
+        raise KernelError("moe_experts: the grouped products need the per-expert counts of moe_route (expert_count)")
     parts = ws.take((top, T, D), torch.bfloat16 if grouped else torch.float32)
     if ok and T <= MOE_ROWS_MAX_TOKENS and D % 256 == 0 and Fd % 256 == 0:
         act = ws.take((T * top, Fd), torch.bfloat16)
@@ -518,15 +528,14 @@ def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, 
         tiles = _moe_tiles(T * top, E)
         rows = tiles * 128
         tile_group = ws.take((tiles,), torch.int32)
-        row_pair = ws.take((rows,), torch.int32)
+        cursor = ws.take((E,), torch.int32)
         row_dest = ws.take((rows,), torch.int32)
         row_scale = ws.take((rows,), torch.float32)
         a_sorted = ws.take((rows, D), torch.bfloat16)
         act = ws.take((rows, Fd), torch.bfloat16)
-        _check(lib().aien_moe_sort_pairs(_p(ids), _p(wts), T, top, E, tiles, _p(tile_group), _p(row_pair), _p(row_dest),
-                                         _p(row_scale), _stream()), "moe_sort_pairs")
-        _check(lib().aien_moe_gather_rows(_p(h), h.stride(0), _p(row_pair), _p(tile_group), top, _p(a_sorted), D, rows, _stream()),
-               "moe_gather_rows")
+        _check(lib().aien_moe_plan_rows(_p(expert_count), E, tiles, _p(cursor), _p(tile_group), _p(row_dest), _stream()), "moe_plan_rows")
+        _check(lib().aien_moe_place_rows(_p(h), h.stride(0), _p(ids), _p(wts), _p(cursor), T, top, _p(a_sorted), D, _p(row_dest),
+                                         _p(row_scale), _stream()), "moe_place_rows")
         _check(lib().aien_gemm_tc_grouped(_p(a_sorted), D, _p(w_up), D, E, _p(act), BF16, Fd, _p(tile_group), tiles, None, None,
                                           Fd, D, 2 + int(act_kind), _stream()), "gemm_tc_grouped(up)")
         _check(lib().aien_gemm_tc_grouped(_p(act), Fd, _p(w_down), Fd, E, _p(parts), BF16, D, _p(tile_group), tiles, _p(row_dest),

@@ -42,7 +42,7 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"group_keep {self.group_keep} of {G} groups")
         if not (0 < self.top <= self.group_keep * (E // G)):
             raise ValueError(f"top {self.top} exceeds the {self.group_keep * (E // G)} experts that stay eligible")
-        self.w_router = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = None
+        self.w_router = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = self.expert_count = None
 
     def param_shapes(self):
         H, F = self.hidden_size, self.expert_ff
@@ -66,6 +66,8 @@ class RoutedExperts(FeedForward):
             ups, downs = [t.float() for t in ups], [t.float() for t in downs]
         self.w_up = torch.stack(ups, dim=0).contiguous()                # [E, F, H]
         self.w_down = torch.stack(downs, dim=0).contiguous()            # [E, H, F]
+        # choices per expert: the router's kernel counts, the plan of the grouped products reads and zeroes them again
+        self.expert_count = torch.zeros(self.num_experts, dtype=torch.int32, device=self.w_up.device)
         if self.shared_ff:
             self.w_shared_up = tensors["shared.up"].contiguous()
             self.w_shared_down = tensors["shared.down"].contiguous()
@@ -86,8 +88,9 @@ class RoutedExperts(FeedForward):
             K.gemm_simple(h, self.w_router, z)                          # float32 operands, float32 sums
         ids = ws.take((T, top), torch.int32)
         wts = ws.take((T, top), torch.float32)
-        K.moe_route(z, self.group_count, self.group_keep, top, self.renormalise, ids, wts)
-        parts = K.moe_experts(ctx, h, self.w_up, self.w_down, ids, wts, top, self.act)
+        counts = self.expert_count if K.moe_takes_grouped(h, self.w_up, self.w_down) else None
+        K.moe_route(z, self.group_count, self.group_keep, top, self.renormalise, ids, wts, counts)
+        parts = K.moe_experts(ctx, h, self.w_up, self.w_down, ids, wts, top, self.act, counts)
         shared = None
         if self.shared_ff:
             a = linear(ctx, h, self.w_shared_up, act=self.shared_act)          # the activation in the product's epilogue
