@@ -241,9 +241,14 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     griddep_launch();
     griddep_wait();
-    const int group = __ldcg(tile_group + blockIdx.x);
+    // column tiles fastest: the CTAs that run together share a row tile of A and walk one expert's W, so both come
+    // from HBM once (row tiles fastest read A again for every column tile once W had pushed it out of L2: 400 MB
+    // of DRAM reads for 250 MB of operands)
+    const int n_tiles = (N + BN - 1) / BN;
+    const int m_tile = (int)(blockIdx.x / n_tiles), n_tile = (int)(blockIdx.x % n_tiles);
+    const int group = __ldcg(tile_group + m_tile);
     if (group < 0) return;                               // the whole CTA: nothing was allocated yet
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
     const int w0 = group * N + n0;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
 
@@ -339,7 +344,7 @@ static int launch_tc_grouped(const void* A, long lda, int rows_a, const void* W,
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcT<128, 128>::SMEM) != cudaSuccess) return AIEN_E_STATE;
         configured = true;
     }
-    dim3 grid(tiles, (N + 127) / 128);
+    dim3 grid((unsigned)((long)tiles * ((N + 127) / 128)));
     launch_chain(kern, grid, dim3(192), (size_t)TcT<128, 128>::SMEM, stream, ma, mw, (TC*)out, ldc, tile_group, row_dest, row_scale, N, K);
     return launch_status();
 }
@@ -882,7 +887,7 @@ AIEN_API int aien_gemm_tc_grouped(const void* A, long lda, const void* W, long l
     if (K <= 0 || (K & 7) || groups <= 0 || tile_group == nullptr) return AIEN_E_SHAPE;
     if ((row_dest == nullptr) != (row_scale == nullptr)) return AIEN_E_SHAPE;
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
-    if ((N + 127) / 128 > 65535 || (long)groups * N > 2147483647L) return AIEN_E_SHAPE;
+    if ((long)tiles * ((N + 127) / 128) > 2147483647L || (long)groups * N > 2147483647L) return AIEN_E_SHAPE;
     const int rows_a = tiles * 128;
 #define TCG_CASE(EPIV, T) return launch_tc_grouped<EPIV, T>(A, lda, rows_a, W, ldw, groups, out, ldc, tile_group, tiles, row_dest, row_scale, N, K, stream)
     if (c_dt == AIEN_DT_BF16) {
