@@ -94,5 +94,6 @@ class RoutedExperts(FeedForward):
         shared = None
         if self.shared_ff:
             a = linear(ctx, h, self.w_shared_up, act=self.shared_act)          # the activation in the product's epilogue
-            shared = linear(ctx, a, self.w_shared_down, out_dtype=torch.float32, may_defer_sum=True)
+            # beside bfloat16 routed parts (the grouped products) the shared expert's output is bfloat16 too; else float32
+            shared = linear(ctx, a, self.w_shared_down, out_dtype=torch.bfloat16 if counts is not None else torch.float32, may_defer_sum=True)
         return parts, shared
