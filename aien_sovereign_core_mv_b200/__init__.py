@@ -1,4 +1,4 @@
-"""A small, whole inference engine for the dense Llama / Qwen3 decoder on one B200 (sm_100a).
+"""A small, whole inference engine for the dense Llama / Qwen3 decoder and the Dulisun design on one B200 (sm_100a).
 
 Public surface: :class:`Engine` (model + cache + step), :class:`EngineConfig`,
 ``generate`` (Python entry point), the registries for architectures and parts, and the weight

@@ -111,7 +111,7 @@ def cmd_info(args) -> int:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="aien-b200", description="B200 inference engine for the dense Llama / Qwen3 decoder")
+    ap = argparse.ArgumentParser(prog="aien-b200", description="B200 inference engine for the dense Llama / Qwen3 decoder and the Dulisun design")
     sub = ap.add_subparsers(dest="command", required=True)
     g = sub.add_parser("generate", help="generate token ids from prompt token ids")
     _engine_args(g)
