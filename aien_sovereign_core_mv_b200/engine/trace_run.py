@@ -30,7 +30,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="tokens the cache pool holds")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
-    ap.add_argument("--max-requests", type=int, default=8, help="requests live at a time (default 8)")
+    ap.add_argument("--max-requests", type=int, default=4, help="requests live at a time: rows of the block tables and state slots (default 4)")
     args = ap.parse_args(argv)
 
     print("trace_run: loading the engine (native code is compiled at first use)", file=sys.stderr, flush=True)

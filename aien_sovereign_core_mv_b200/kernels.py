@@ -158,6 +158,17 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
         "aien_attention_decode_stream_error": [],
         "aien_collect_wait_errors": [P, P],
+        "aien_decay_linear_attention": [P, I, L, I, I, I, P, P, P, P, P, P, L, I, I, I, I, P],
+        "aien_gated_rmsnorm": [P, L, P, I, L, P, I, F, P, I, L, I, I, P],
+        "aien_gated_recurrence": [P, I, L, I, I, I, P, P, I, P, P, P, P, P, I, L, I, I, P],
+        "aien_latent_prepare": [P, I, L, I, P, P, I, F, P, I, L, I, I, I, I, P, P, P, P, I, I, P],
+        "aien_rotate_pairs_rows": [P, I, L, L, P, L, L, I, I, I, I, P, P, P],
+        "aien_head_project": [P, I, L, L, P, I, L, L, P, I, L, L, I, I, I, I, P],
+        "aien_latent_attention": [P, L, P, I, P, I, P, P, P, P, I, L, I, I, I, I, I, I, F, P, P],
+        "aien_post_norm_add": [P, P, I, I, c_size_t, P, I, F, F, P, I, F, P, I, I, I, P],
+        "aien_embed_gather_scaled": [P, I, P, P, I, I, I, F, P],
+        "aien_gelu_times_table": [P, I, L, P, I, L, I, P, I, P, I, L, I, I, P],
+        "aien_softcap": [P, c_size_t, F, P],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
     }
@@ -1165,3 +1176,173 @@ def wait_error_message(words) -> str:
         return ""
     return ("a bounded wait ran out inside " + ", ".join(bad) +
             ": the results of the step are not valid (a broken TMA / tensor-core pipeline, not a property of the inputs)")
+
+
+# ---------------------------------------------------------------------------- norms around a sublayer, scaled ends
+def embed_gather_scaled(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, scale: float) -> None:
+    """x[t] = table[ids[t]] * scale as float32."""
+    _dev(table, ids, x)
+    T, H = x.shape
+    assert table.is_contiguous() and x.is_contiguous() and ids.dtype == torch.int32 and x.dtype == torch.float32
+    assert table.shape[1] == H and ids.numel() >= T
+    _check(lib().aien_embed_gather_scaled(_p(table), dt(table), _p(ids), _p(x), T, H, table.shape[0], float(scale), _stream()),
+           "embed_gather_scaled")
+
+
+def post_norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, mult: float = 1.0,
+                  next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0, h: Optional[torch.Tensor] = None) -> None:
+    """x += mult * y / sqrt(mean(y^2) + eps) * weight with y = a ([T,H], or float32 parts [P,T,H] added in order), in
+    float32; then ``h`` (optional, [T,H]) = x / sqrt(mean(x^2) + next_eps) * next_weight, or the plain copy of the new
+    x when ``next_weight`` is None."""
+    _dev(x, a, weight, next_weight, h)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.numel() == H and weight.is_contiguous()
+    assert next_weight is None or (next_weight.numel() == H and next_weight.is_contiguous() and h is not None)
+    assert h is None or (h.is_contiguous() and tuple(h.shape) == (T, H))
+    pa, da, na, sa = _source(a, x.shape)
+    _check(lib().aien_post_norm_add(_p(x), pa, da, na, sa, _p(weight), dt(weight), float(eps), float(mult), _p(next_weight),
+                                    dt(next_weight) if next_weight is not None else F32, float(next_eps), _p(h),
+                                    dt(h) if h is not None else F32, T, H, _stream()), "post_norm_add")
+
+
+def gelu_times_table(z: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j] for the n columns of out."""
+    _dev(z, table, ids, out)
+    T, n = out.shape
+    assert z.shape == (T, n) and z.stride(1) == 1 and out.stride(1) == 1 and table.is_contiguous() and table.dim() == 2
+    assert 0 <= col0 and col0 + n <= table.shape[1] and ids.dtype == torch.int32 and ids.numel() >= T
+    _check(lib().aien_gelu_times_table(_p(z), dt(z), z.stride(0), _p(table), dt(table), table.shape[1], int(col0), _p(ids),
+                                       table.shape[0], _p(out), dt(out), out.stride(0), T, n, _stream()), "gelu_times_table")
+
+
+def softcap(v: torch.Tensor, cap: float) -> None:
+    """v = cap * tanh(v / cap) in place (float32)."""
+    _dev(v)
+    assert v.dtype == torch.float32 and v.is_contiguous()
+    _check(lib().aien_softcap(_p(v), v.numel(), float(cap), _stream()), "softcap")
+
+
+# ---------------------------------------------------------------------------- mixers with a state of fixed size
+def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
+                           slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                           num_seqs: int, heads: int, dim: int, vdim: int) -> None:
+    """Per head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v = silu of the columns of ``proj`` [T, *]
+    at q_off (heads*dim), k_off (heads*dim), v_off (heads*vdim).  ``state`` float32 [slots, heads, dim, vdim]: request s
+    of the step (tokens q_start[s]..q_start[s+1]) continues from slot slot_map[s], from zero when its first token has
+    position 0, and leaves its state there.  ``out`` float32 [T, heads*vdim]."""
+    _dev(proj, decay, state, slot_map, q_start, positions, out)
+    assert proj.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == heads * vdim
+    assert decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+    for t in (slot_map, q_start, positions):
+        assert t.dtype == torch.int32
+    assert max(q_off, k_off) + heads * dim <= proj.shape[1] and v_off + heads * vdim <= proj.shape[1]
+    _check(lib().aien_decay_linear_attention(_p(proj), dt(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _p(decay),
+                                             _p(state), _p(slot_map), _p(q_start), _p(positions), _p(out), out.stride(0),
+                                             int(num_seqs), int(heads), int(dim), int(vdim), _stream()), "decay_linear_attention")
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * weight * sigmoid(gate[t]); o float32 [T,N], gate [T,N] (row stride free)."""
+    _dev(o, gate, weight, out)
+    T, N = o.shape
+    assert o.dtype == torch.float32 and o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
+    assert tuple(gate.shape) == (T, N) and tuple(out.shape) == (T, N) and weight.numel() == N and weight.is_contiguous()
+    _check(lib().aien_gated_rmsnorm(_p(o), o.stride(0), _p(gate), dt(gate), gate.stride(0), _p(weight), dt(weight), float(eps),
+                                    _p(out), dt(out), out.stride(0), T, N, _stream()), "gated_rmsnorm")
+
+
+def gated_recurrence(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Optional[torch.Tensor], bx: Optional[torch.Tensor],
+                     state: torch.Tensor, slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                     num_seqs: int, width: int) -> None:
+    """Per channel S_t = (1 - z) S_(t-1) + z c with z = sigmoid(proj[z] + bz), u = proj[x] + bx, c = u + 1/2 (u >= 0) or
+    sigmoid(u) (u < 0); out_t = S_t * silu(proj[g]).  ``state`` float32 [slots, width], slots as in decay_linear_attention."""
+    _dev(proj, bz, bx, state, slot_map, q_start, positions, out)
+    assert proj.stride(1) == 1 and out.stride(1) == 1 and out.shape[1] == width
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width
+    assert max(z_off, x_off, g_off) + width <= proj.shape[1]
+    bdt = F32
+    for b in (bz, bx):
+        if b is not None:
+            assert b.numel() == width and b.is_contiguous()
+            bdt = dt(b)
+    assert bz is None or bx is None or bz.dtype == bx.dtype
+    for t in (slot_map, q_start, positions):
+        assert t.dtype == torch.int32
+    _check(lib().aien_gated_recurrence(_p(proj), dt(proj), proj.stride(0), int(z_off), int(x_off), int(g_off), _p(bz), _p(bx), bdt,
+                                       _p(state), _p(slot_map), _p(q_start), _p(positions), _p(out), dt(out), out.stride(0),
+                                       int(num_seqs), int(width), _stream()), "gated_recurrence")
+
+
+# ---------------------------------------------------------------------------- attention over a cached latent
+def latent_prepare(d: torch.Tensor, q_rank: int, wq: Optional[torch.Tensor], eps: float, cq: Optional[torch.Tensor],
+                   kv_off: int = 0, kv_rank: int = 0, rot_dim: int = 0, rot_dims: int = 0, wkv: Optional[torch.Tensor] = None,
+                   cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                   slot_map: Optional[torch.Tensor] = None, cache: Optional[torch.Tensor] = None) -> None:
+    """From the down projections d [T, *] (float32): cq = RMS norm of the first ``q_rank`` columns times ``wq``; and, with
+    ``cache`` [slots, kv_rank + rot_dim], the token's cache row = RMS norm of the ``kv_rank`` columns at ``kv_off`` times
+    ``wkv``, then the next ``rot_dim`` columns with their first ``rot_dims`` rotated in neighbouring pairs."""
+    _dev(d, wq, cq, wkv, cos, sin, slot_map, cache)
+    T = d.shape[0]
+    assert d.stride(1) == 1 and (q_rank == 0 or (cq is not None and cq.stride(1) == 1 and wq is not None and wq.numel() == q_rank))
+    wdt = F32
+    for w in (wq, wkv):
+        if w is not None:
+            assert w.is_contiguous()
+            wdt = dt(w)
+    assert wq is None or wkv is None or wq.dtype == wkv.dtype
+    if cache is not None:
+        assert cache.is_contiguous() and cache.shape[-1] == kv_rank + rot_dim and wkv is not None and wkv.numel() == kv_rank
+        assert slot_map is not None and slot_map.dtype == torch.int32 and slot_map.numel() >= T
+        assert kv_off + kv_rank + rot_dim <= d.shape[1]
+        if rot_dims:
+            assert cos is not None and tuple(cos.shape) == (T, rot_dims // 2) and cos.is_contiguous() and sin.is_contiguous()
+    _check(lib().aien_latent_prepare(_p(d), dt(d), d.stride(0), int(q_rank), _p(wq), _p(wkv), wdt, float(eps), _p(cq),
+                                     dt(cq) if cq is not None else F32, cq.stride(0) if cq is not None else 0, int(kv_off),
+                                     int(kv_rank), int(rot_dim), int(rot_dims), _p(cos), _p(sin), _p(slot_map), _p(cache),
+                                     dt(cache) if cache is not None else F32, T, _stream()), "latent_prepare")
+
+
+def rotate_pairs_rows(q: torch.Tensor, q_head: int, col0: int, out: torch.Tensor, o_head: int, ocol0: int, heads: int, rot_dim: int,
+                      rot_dims: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor]) -> None:
+    """out[t, h*o_head + ocol0 + i] = q[t, h*q_head + col0 + i], i < rot_dim, the first ``rot_dims`` of them rotated in
+    neighbouring pairs by the token's angle; out float32."""
+    _dev(q, out, cos, sin)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == torch.float32
+    if rot_dims:
+        assert cos is not None and tuple(cos.shape) == (T, rot_dims // 2) and cos.is_contiguous() and sin.is_contiguous()
+    qv, ov = q[:, col0:], out[:, ocol0:]
+    _check(lib().aien_rotate_pairs_rows(_p(qv), dt(q), q.stride(0), int(q_head), _p(ov), out.stride(0), int(o_head), T, int(heads),
+                                        int(rot_dim), int(rot_dims), _p(cos), _p(sin), _stream()), "rotate_pairs_rows")
+
+
+def head_project(a: torch.Tensor, a_head: int, a_col0: int, w: torch.Tensor, out: torch.Tensor, o_head: int, o_col0: int) -> None:
+    """out[t, h*o_head + o_col0 + n] = sum_k a[t, h*a_head + a_col0 + k] * w[h, n, k]: one product per head, w [heads, N, K]."""
+    _dev(a, w, out)
+    heads, N, K_ = w.shape
+    M = a.shape[0]
+    assert a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous() and out.shape[0] == M
+    assert (heads - 1) * a_head + a_col0 + K_ <= a.shape[1] and (heads - 1) * o_head + o_col0 + N <= out.shape[1]
+    av, ov = a[:, a_col0:], out[:, o_col0:]
+    _check(lib().aien_head_project(_p(av), dt(a), a.stride(0), int(a_head), _p(w), dt(w), K_, N * K_, _p(ov), dt(out), out.stride(0),
+                                   int(o_head), M, N, K_, heads, _stream()), "head_project")
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, max_blocks: int, seq_of_token: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, heads: int, kv_rank: int, rot_dim: int, page_size: int,
+                     window: int, scale: float, sinks: Optional[torch.Tensor]) -> None:
+    """Attention of the step's tokens over cached latent rows [slots, kv_rank + rot_dim] shared by all heads: q float32
+    [T, heads*(kv_rank + rot_dim)], out [T, heads*kv_rank] = the softmax-weighted sums of the rows' first kv_rank numbers.
+    ``window`` > 0: a token sees itself and the window - 1 tokens before it.  ``sinks`` float32 [heads] or None."""
+    _dev(q, cache, block_table, seq_of_token, positions, out, sinks)
+    T = q.shape[0]
+    D = kv_rank + rot_dim
+    assert q.dtype == torch.float32 and q.stride(1) == 1 and q.shape[1] == heads * D and out.stride(1) == 1
+    assert out.shape == (T, heads * kv_rank) and cache.is_contiguous() and cache.shape[-1] == D
+    assert block_table.dtype == torch.int32 and seq_of_token.dtype == torch.int32 and positions.dtype == torch.int32
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == heads)
+    _check(lib().aien_latent_attention(_p(q), q.stride(0), _p(cache), dt(cache), _p(block_table), int(max_blocks), _p(seq_of_token),
+                                       _p(positions), None, _p(out), dt(out), out.stride(0), T, int(heads), int(kv_rank),
+                                       int(rot_dim), int(page_size), int(window), float(scale), _p(sinks), _stream()),
+           "latent_attention")

@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import Prenormed, Block, CacheNeed, Mixer, RunBinding, StepContext, StreamCopy
+from ..parts.base import Prenormed, Block, CacheNeed, Mixer, NormedStream, RunBinding, StepContext, StreamCopy
 from ..registry import make_part, part_factory
 
 
@@ -159,6 +159,10 @@ class Decoder:
                 waiting.discard((li, pname))
         if self.tied:
             self.head.tie(self.embedding)
+        for block in self.blocks:                       # parts that read a table the embedding owns
+            for part in block.parts().values():
+                if hasattr(part, "tie_embedding"):
+                    part.tie_embedding(self.embedding)
         if pending or waiting:
             raise RuntimeError("bind: some parts did not receive all their tensors")
 
@@ -193,7 +197,7 @@ class Decoder:
             else:
                 delta = block.forward(ctx, x, delta, binding)
         ws.end_layers()
-        if isinstance(delta, (Prenormed, StreamCopy)):    # nothing is pending: the last block summed into the stream itself
+        if isinstance(delta, (Prenormed, StreamCopy, NormedStream)):    # nothing is pending: the last block summed into the stream itself
             delta = None
         if num_rows > 0:
             rows = ws.take((num_rows, self.hidden_size), torch.float32)

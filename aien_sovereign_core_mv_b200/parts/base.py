@@ -218,6 +218,16 @@ class StreamCopy:
 
 
 @dataclass
+class NormedStream:
+    """What a block hands on when its last kernel already made the next block's first norm: nothing is
+    pending, and ``h`` = ``norm``(stream) in the compute dtype.  The block whose first norm is ``norm``
+    takes ``h`` as its mixer's input; every other consumer treats it as "nothing pending"."""
+
+    h: torch.Tensor
+    norm: "Norm"
+
+
+@dataclass
 class ResidualSink:
     """Offered to a part whose last product ends a residual branch: instead of returning the
     branch's output for the next norm to add, the product may add it to ``x`` itself and return a
@@ -325,7 +335,7 @@ def add_to_residual(ctx: StepContext, x: torch.Tensor, delta) -> None:
     partial products [P, T, H], or a Prenormed (whose sum is in x already).  For blocks that do
     not fuse the residual sum into a norm."""
     from .. import kernels as K
-    if delta is None or isinstance(delta, (Prenormed, StreamCopy)):
+    if delta is None or isinstance(delta, (Prenormed, StreamCopy, NormedStream)):
         return
     K.add_residual(x, delta)
 

@@ -15,23 +15,43 @@ from .linear import linear
 class TableEmbedding(Embedding):
     """x[t] = weight[token_ids[t]], widened to float32 (crates/aien-inference-abi/src/
     transformer_backend.rs:1179-1181, src/weights.rs:140-146; ids are checked against the
-    vocabulary before a step is accepted instead of being reduced modulo it)."""
+    vocabulary before a step is accepted instead of being reduced modulo it).
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    ``scale``: the row is multiplied by this constant.  ``side_width`` > 0: the part also owns a second table
+    ``side`` [vocab, side_width] that it does not read itself; layers with a per-token side input take their columns
+    of it (``side_table``)."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, side_width: int = 0):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.scale, self.side_width = float(scale), int(side_width)
         self.weight: Optional[torch.Tensor] = None
+        self.side: Optional[torch.Tensor] = None
 
     def param_shapes(self):
-        return {"weight": ((self.vocab_size, self.hidden_size), "embedding")}
+        shapes = {"weight": ((self.vocab_size, self.hidden_size), "embedding")}
+        if self.side_width > 0:
+            shapes["side"] = ((self.vocab_size, self.side_width), "embedding")
+        return shapes
 
     def bind(self, tensors):
         self.weight = tensors["weight"].contiguous()
+        if self.side_width > 0:
+            self.side = tensors["side"].contiguous()
 
     def tied_weight(self):
         return self.weight
 
+    def side_table(self) -> Optional[torch.Tensor]:
+        return self.side
+
+    def _gather(self, token_ids: torch.Tensor, x: torch.Tensor) -> None:
+        if self.scale != 1.0:
+            K.embed_gather_scaled(self.weight, token_ids, x, self.scale)
+        else:
+            K.embed_gather(self.weight, token_ids, x)
+
     def forward(self, ctx: StepContext, token_ids: torch.Tensor, x: torch.Tensor) -> None:
-        K.embed_gather(self.weight, token_ids, x)
+        self._gather(token_ids, x)
 
 
 @register_embedding("table_normed")
@@ -41,8 +61,8 @@ class NormedTableEmbedding(TableEmbedding):
     its tensors are this part's ``norm.<local name>``.  A head tied to this embedding multiplies
     by the table itself."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, norm: dict):
-        super().__init__(vocab_size, hidden_size)
+    def __init__(self, vocab_size: int, hidden_size: int, norm: dict, scale: float = 1.0, side_width: int = 0):
+        super().__init__(vocab_size, hidden_size, scale, side_width)
         params = {k: v for k, v in dict(norm).items() if k != "kind"}
         self.norm = make_part("norm", norm["kind"], size=self.hidden_size, **params)
         if not hasattr(self.norm, "norm_stream"):
@@ -59,7 +79,7 @@ class NormedTableEmbedding(TableEmbedding):
         self.norm.bind({k[len("norm."):]: v for k, v in tensors.items() if k.startswith("norm.")})
 
     def forward(self, ctx: StepContext, token_ids: torch.Tensor, x: torch.Tensor) -> None:
-        K.embed_gather(self.weight, token_ids, x)
+        self._gather(token_ids, x)
         self.norm.norm_stream(ctx, x)
 
 
@@ -67,10 +87,11 @@ class NormedTableEmbedding(TableEmbedding):
 class LinearHead(Head):
     """logits = rows . W^T with W = ``weight`` [vocab, hidden], or the embedding's table when
     tied: the same buffer, no copy (crates/aien-inference-abi/src/weights.rs:131-136,
-    src/transformer_backend.rs:1370-1386)."""
+    src/transformer_backend.rs:1370-1386).  ``softcap`` c > 0: logits = c * tanh(logits / c), in float32."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False):
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, softcap: float = 0.0):
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.softcap = float(softcap or 0.0)
         self.weight: Optional[torch.Tensor] = None
 
     def param_shapes(self):
@@ -87,3 +108,5 @@ class LinearHead(Head):
 
     def forward(self, ctx: StepContext, rows: torch.Tensor, logits: torch.Tensor) -> None:
         linear(ctx, rows, self.weight, out=logits)
+        if self.softcap > 0.0:
+            K.softcap(logits, self.softcap)

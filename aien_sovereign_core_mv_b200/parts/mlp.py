@@ -62,3 +62,30 @@ class SwiGLU(FeedForward):
             gu = linear(ctx, h, self.w_gate_up)
             K.swiglu(gu, act, self.group)
         return linear_into_residual(ctx, act, self.w_down, sink) or linear(ctx, act, self.w_down, may_defer_sum=True)
+
+
+@register_feed_forward("mlp_act")
+class ActMLP(FeedForward):
+    """y = W_down act(W_up h), no gate and no bias; ``act``: "gelu_tanh" or "gelu" (the erf form).  The activation runs
+    in the first product's epilogue where the kernel has one."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, act: str = "gelu_tanh"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if act not in K.ACT_KINDS:
+            raise ValueError(f"activation {act!r}: known are {sorted(K.ACT_KINDS)}")
+        self.act = K.ACT_KINDS[act]
+        self.w_up = self.w_down = None
+
+    def param_shapes(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return {"up": ((I, H), "matrix"), "down": ((H, I), "matrix")}
+
+    def bind(self, tensors):
+        self.w_up, self.w_down = tensors["up"].contiguous(), tensors["down"].contiguous()
+
+    def workspace_bytes(self, lim):
+        return lim.max_tokens * (self.intermediate_size * lim.itemsize + self.hidden_size * 4) + 4096
+
+    def forward(self, ctx: StepContext, h: torch.Tensor):
+        a = linear(ctx, h, self.w_up, act=self.act)
+        return linear(ctx, a, self.w_down, out_dtype=torch.float32)

@@ -7,7 +7,7 @@ import torch
 
 from .. import kernels as K
 from ..registry import register_norm
-from .base import Norm, Prenormed, ResidualSink, StepContext, StreamCopy
+from .base import Norm, NormedStream, Prenormed, ResidualSink, StepContext, StreamCopy
 
 # AIEN_B200_FUSED_NORM=0 keeps every norm in its own kernel
 _FUSE = __import__("os").environ.get("AIEN_B200_FUSED_NORM", "1").strip() not in ("0", "off", "no")
@@ -50,6 +50,21 @@ class RMSNorm(Norm):
         K.branch_norm_add(x, a, self.weight, self.eps, b=b, h=h)
         return (h if h is not None else x) if want_copy else None
 
+    def add_normed_scaled(self, ctx: StepContext, x: torch.Tensor, a, mult: float, then=None, want_copy: bool = False):
+        """x += mult * norm(a) in float32, and in the same kernel what the next sublayer reads: ``then`` (a norm of this
+        kind) gives then(x) in the compute dtype; ``want_copy`` the stream's compute-dtype copy (x itself in float32).
+        Returns that tensor, or None when neither was asked.  A ``then`` of another kind is applied by its own kernel."""
+        fused = then is not None and type(then) is RMSNorm
+        h = None
+        if fused or (want_copy and ctx.dtype != torch.float32):
+            h = ctx.workspace.take(tuple(x.shape), ctx.dtype)
+        K.post_norm_add(x, a, self.weight, self.eps, mult, then.weight if fused else None, then.eps if fused else 0.0, h)
+        if fused:
+            return h
+        if then is not None:
+            return then.forward(ctx, x, None)
+        return (h if h is not None else x) if want_copy else None
+
     def norm_stream(self, ctx: StepContext, x: torch.Tensor, want_copy: bool = False):
         """x = norm(x) in place; with ``want_copy`` also the compute-dtype copy (x itself in float32)."""
         h = self._copy_for(ctx, x, want_copy)
@@ -68,6 +83,10 @@ class RMSNorm(Norm):
             if delta.norm is self:
                 return delta                      # the sum is in x already; the consumer finishes the norm
             delta = None                          # made for another norm: x is up to date, norm it here
+        if isinstance(delta, NormedStream):
+            if delta.norm is self:
+                return delta.h                    # made by the kernel that wrote the last sum
+            delta = None
         if isinstance(delta, StreamCopy):
             delta = None                          # nothing pending
         out = ctx.workspace.take(tuple(x.shape), ctx.dtype)

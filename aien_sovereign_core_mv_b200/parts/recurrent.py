@@ -1,0 +1,107 @@
+"""Mixers that keep a state of fixed size per request instead of keys and values."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_mixer
+from .base import CacheNeed, Mixer, RunBinding, StepContext
+from .linear import linear
+
+
+@register_mixer("decay_linear_attention")
+class DecayLinearAttention(Mixer):
+    """Linear attention with one decay per head: q = silu(W_q h), k = silu(W_k h) (heads x ``head_dim``), v = silu(W_v h)
+    (heads x ``value_dim``); per head S_t = decay_h S_(t-1) + k_t v_t^T and o_t = S_t^T q_t, with no other scale.  The
+    heads together pass an RMS norm (plain weight ``norm``), are multiplied by sigmoid(W_g h) and projected by W_o.
+    The state [heads, head_dim, value_dim] is float32, starts at zero and is carried in a state slot of the cache; the
+    recurrence, its decay powers and the norm are float32 in both engine precisions.  One product makes q | k | v | g."""
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, decay: Sequence[float],
+                 norm_eps: float = 1e-6, position=None):
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = int(hidden_size), int(num_heads), int(head_dim), int(value_dim)
+        self.decay_values = [float(d) for d in decay]
+        if len(self.decay_values) != self.num_heads:
+            raise ValueError(f"decay names {len(self.decay_values)} values for {self.num_heads} heads")
+        if any(not (0.0 <= d <= 1.0) for d in self.decay_values):
+            raise ValueError("every decay must lie in [0, 1]")
+        self.norm_eps = float(norm_eps)
+        self.qk_dim, self.v_dim = self.num_heads * self.head_dim, self.num_heads * self.value_dim
+        self.w_in = self.w_o = self.norm_w = self.decay = None
+
+    def param_shapes(self):
+        H = self.hidden_size
+        return {"q_proj": ((self.qk_dim, H), "matrix"), "k_proj": ((self.qk_dim, H), "matrix"), "v_proj": ((self.v_dim, H), "matrix"),
+                "g_proj": ((self.v_dim, H), "matrix"), "o_proj": ((H, self.v_dim), "matrix"), "norm": ((self.v_dim,), "norm")}
+
+    def bind(self, tensors):
+        rows = [tensors[n] for n in ("q_proj", "k_proj", "v_proj", "g_proj")]
+        if len({t.dtype for t in rows}) > 1:
+            rows = [t.float() for t in rows]
+        self.w_in = torch.cat(rows, dim=0).contiguous()                 # rows q | k | v | g
+        self.w_o = tensors["o_proj"].contiguous()
+        self.norm_w = tensors["norm"].contiguous()
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.w_o.device)
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.num_heads, self.head_dim, self.value_dim), state_dtype="float32")
+
+    def workspace_bytes(self, lim):
+        return lim.max_tokens * ((2 * self.qk_dim + 2 * self.v_dim) * 4 + self.v_dim * (4 + lim.itemsize) + self.hidden_size * 4) + 8192
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
+        T = ctx.num_tokens
+        group = ctx.groups[run.group]
+        state = group.storage["state"][run.slot]
+        proj = linear(ctx, h, self.w_in, out_dtype=torch.float32)
+        o = ctx.workspace.take((T, self.v_dim), torch.float32)
+        K.decay_linear_attention(proj, 0, self.qk_dim, 2 * self.qk_dim, self.decay, state, group.slot_map, ctx.q_start, ctx.positions,
+                                 o, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim)
+        y = ctx.workspace.take((T, self.v_dim), ctx.dtype)
+        K.gated_rmsnorm(o, proj[:, 2 * self.qk_dim + self.v_dim:], self.norm_w, self.norm_eps, y)
+        return linear(ctx, y, self.w_o, out_dtype=torch.float32)
+
+
+@register_mixer("gated_recurrence")
+class GatedRecurrence(Mixer):
+    """A gated recurrence over ``width`` channels whose gates read only the current token: z = sigmoid(W_z h + b_z),
+    u = W_x h + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u) where u < 0; S_t = (1 - z) S_(t-1) + z c element
+    by element; output W_o (S_t * silu(W_g h)).  The state [width] is float32, starts at zero and is carried in a state
+    slot of the cache; gates, candidate and state are float32 in both engine precisions.  One product makes z | u | g."""
+
+    def __init__(self, hidden_size: int, width: int, bias: bool = True, position=None):
+        self.hidden_size, self.width, self.bias = int(hidden_size), int(width), bool(bias)
+        self.w_in = self.w_o = self.b_z = self.b_x = None
+
+    def param_shapes(self):
+        H, W = self.hidden_size, self.width
+        shapes = {"z_proj": ((W, H), "matrix"), "x_proj": ((W, H), "matrix"), "g_proj": ((W, H), "matrix"), "o_proj": ((H, W), "matrix")}
+        if self.bias:
+            shapes.update({"z_bias": ((W,), "vector"), "x_bias": ((W,), "vector")})
+        return shapes
+
+    def bind(self, tensors):
+        rows = [tensors[n] for n in ("z_proj", "x_proj", "g_proj")]
+        if len({t.dtype for t in rows}) > 1:
+            rows = [t.float() for t in rows]
+        self.w_in = torch.cat(rows, dim=0).contiguous()                 # rows z | u | g
+        self.w_o = tensors["o_proj"].contiguous()
+        if self.bias:
+            self.b_z, self.b_x = tensors["z_bias"].float().contiguous(), tensors["x_bias"].float().contiguous()
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.width,), state_dtype="float32")
+
+    def workspace_bytes(self, lim):
+        return lim.max_tokens * (3 * self.width * 4 + self.width * lim.itemsize + self.hidden_size * 4) + 8192
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
+        T, W = ctx.num_tokens, self.width
+        group = ctx.groups[run.group]
+        state = group.storage["state"][run.slot]
+        proj = linear(ctx, h, self.w_in, out_dtype=torch.float32)
+        y = ctx.workspace.take((T, W), ctx.dtype)
+        K.gated_recurrence(proj, 0, W, 2 * W, self.b_z, self.b_x, state, group.slot_map, ctx.q_start, ctx.positions, y, ctx.num_seqs, W)
+        return linear(ctx, y, self.w_o, out_dtype=torch.float32)

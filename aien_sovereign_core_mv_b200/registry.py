@@ -11,7 +11,7 @@ from typing import Any, Callable, Dict
 
 _ARCHITECTURES: Dict[str, Callable[..., Any]] = {}
 _PARTS: Dict[str, Dict[str, Callable[..., Any]]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "side": {},
 }
 
 
@@ -73,6 +73,11 @@ def register_embedding(kind: str):
 
 def register_head(kind: str):
     return _register("head", kind)
+
+
+def register_side(kind: str):
+    """A per-layer input besides the residual stream (e.g. a second embedding of the token)."""
+    return _register("side", kind)
 
 
 def part_factory(family: str, kind: str):
