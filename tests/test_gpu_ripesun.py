@@ -1,0 +1,547 @@
+"""The Ripesun design in the engine against its plain implementation (``plain_ripesun``): each mechanism alone, then
+whole models under every way of cutting the work, in float32 and bfloat16.
+
+The configurations are small and differ from one another in every size and constant: head counts that fill no warp or
+block of heads evenly, latent sizes that are no multiple of 32, windows of less than a page, of several pages and none,
+two layers that share one cache under different windows, decays of 0 and 1, a layer without a feed-forward, models
+with and without the token side input, the soft cap, the embedding scale and the residual multiplier.  Where random
+weights would hide a fault the inputs are made so that it shows: keys just inside and just outside a window are scaled
+until their scores stand out, a sink is made large, a far key is made the only one that matters.
+"""
+import copy
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_ripesun as pr
+
+pytestmark = pytest.mark.gpu
+
+
+def _latent(heads, dim, rot_dim, vdim, kv_rank, q_rank, window, scale, base=10000.0, kv_from=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": scale,
+         "rot": {"base": base, "dims": rot_dim}, "mask": {"size": window} if window else None}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _light(heads, dim, vdim, decay):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+CONFIGS = {
+    # five heads, latent of 40, windows of 21 and 9 on one shared cache, decays 0.5 / 0.9 / 1, a layer without feed-forward
+    "A": {"architecture": "Ripesun", "vocab": 333, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0},
+          "residual_mult": 0.7, "logit_softcap": 20.0, "token_side": {"dim": 8}, "layers": [
+              {"type": "lightning", "mixer": _light(3, 20, 12, [0.5, 0.9, 1.0]), "mlp": _dense(80)},
+              {"type": "latent_attention", "mixer": _latent(5, 24, 8, 16, 40, 48, 21, 0.2), "mlp": _dense(64)},
+              {"type": "mingru", "mixer": {"width": 72}, "mlp": None},
+              {"type": "latent_attention", "mixer": _latent(5, 12, 8, 20, 40, 24, 9, 0.3, kv_from=1), "mlp": _dense(48)},
+              {"type": "lightning", "mixer": _light(2, 16, 40, [0.0, 0.97]), "mlp": _dense(40)}]},
+    # no side input, no cap, no scale, multiplier 1; one head, a latent of 96, no mask at all (every key stays), a reader of it
+    "B": {"architecture": "Ripesun", "vocab": 257, "width": 64, "norm": {"eps": 3e-6}, "layers": [
+        {"type": "mingru", "mixer": {"width": 100}, "mlp": _dense(96)},
+        {"type": "latent_attention", "mixer": _latent(1, 16, 16, 16, 96, 16, 0, 0.25, 1e6), "mlp": None},
+        {"type": "latent_attention", "mixer": _latent(3, 8, 16, 8, 96, 40, 0, 0.35, 1e6, kv_from=1), "mlp": _dense(72)}]},
+    # sizes the tensor-core products take; 17 heads (two blocks of heads), a window of four pages, a window of one page
+    "C": {"architecture": "Ripesun", "vocab": 512, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0},
+          "residual_mult": 0.5, "logit_softcap": 30.0, "token_side": {"dim": 16}, "layers": [
+              {"type": "latent_attention", "mixer": _latent(17, 64, 32, 64, 128, 64, 64, 0.1, 50000.0), "mlp": _dense(256)},
+              {"type": "lightning", "mixer": _light(4, 64, 64, [0.8, 0.95, 0.99, 0.999]), "mlp": _dense(256)},
+              {"type": "mingru", "mixer": {"width": 256}, "mlp": _dense(128)},
+              {"type": "latent_attention", "mixer": _latent(4, 32, 64, 32, 64, 128, 16, 0.12, 777.0), "mlp": _dense(128)}]},
+}
+PAGE = {"A": 16, "B": 8, "C": 16}
+LENGTHS = {"A": [1, 9, 50, 131], "B": [2, 20, 77], "C": [5, 70, 150]}
+FP32_TOL, BF16_TOL = 1e-4, 4e-2
+DTYPES = [("float32", FP32_TOL), ("bfloat16", BF16_TOL)]
+
+
+def load_plain(folder):
+    from aien_sovereign_core_mv_b200.weights.safetensors_io import CheckpointFiles
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    files = CheckpointFiles(folder)
+    tensors = {n: files.tensor(n).float().numpy().astype(np.float64) for n in files.names()}
+    files.close()
+    return cfg, tensors
+
+
+def tokens(which, n, seed):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, CONFIGS[which]["vocab"], n)]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    from aien_sovereign_core_mv_b200 import write_random_model
+    root = tmp_path_factory.mktemp("ripesun")
+    out = {}
+    for i, which in enumerate(CONFIGS):
+        d = write_random_model(os.path.join(str(root), which), CONFIGS[which], 70 + i)
+        cfg, tensors = load_plain(d)
+        reqs = {j + 1: tokens(which, n, 100 * i + n) for j, n in enumerate(LENGTHS[which])}
+        want = {rid: pr.forward(cfg, tensors, toks) for rid, toks in reqs.items()}
+        out[which] = (d, reqs, want)
+    return out
+
+
+def check(collected, want, tol, what):
+    assert collected, f"{what}: nothing was collected"
+    for rid, rows in collected.items():
+        pos = sorted(rows)
+        got, ref = np.stack([rows[p] for p in pos]), want[rid][pos]
+        H.assert_close(got, ref, tol, f"{what} request {rid} (positions {pos[0]}..{pos[-1]})")
+
+
+def make_ctx(dtype, positions, seq_of_token, q_start, ctx_len, groups=()):
+    from test_gpu_parts import make_ctx as mk
+    return mk(dtype, positions, seq_of_token, q_start, ctx_len, groups)
+
+
+def i32(a):
+    return torch.tensor(a, dtype=torch.int32, device="cuda")
+
+
+# ------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,parts", [(72, 1), (2304, 3), (90, 2)])
+def test_scaled_sum_of_a_normed_branch_and_the_next_norm(dtype, width, parts):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(width)
+    T, eps, eps2, mult = 5, 1e-5, 3e-6, 0.37
+    w = (torch.rand(width, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda()
+    w2 = (torch.rand(width, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda()
+    x0 = torch.randn(T, width, generator=g).cuda()
+    a = torch.randn(parts, T, width, generator=g).cuda() if parts > 1 else torch.randn(T, width, generator=g).to(dtype).cuda()
+    y = a.double().sum(0).cpu().numpy() if parts > 1 else a.double().cpu().numpy()
+    want_x = x0.double().cpu().numpy() + mult * pr.rms_norm(y, w.double().cpu().numpy(), eps)
+    tol_h = 2e-6 if dtype == torch.float32 else 8e-3
+    # the sum and the next norm
+    x, h = x0.clone(), torch.empty(T, width, dtype=dtype).cuda()
+    K.post_norm_add(x, a, w, eps, mult, w2, eps2, h)
+    H.assert_close(x.cpu().numpy(), want_x, 2e-6, "stream")
+    H.assert_close(h.float().cpu().numpy(), pr.rms_norm(want_x, w2.double().cpu().numpy(), eps2), tol_h, "next norm")
+    # the sum and the plain copy; the sum alone
+    x, h = x0.clone(), torch.empty(T, width, dtype=dtype).cuda()
+    K.post_norm_add(x, a, w, eps, mult, None, 0.0, h)
+    H.assert_close(h.float().cpu().numpy(), want_x, tol_h, "copy")
+    x = x0.clone()
+    K.post_norm_add(x, a, w, eps, mult)
+    H.assert_close(x.cpu().numpy(), want_x, 2e-6, "stream alone")
+
+
+def test_scaled_embedding_side_gate_and_soft_cap():
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(50, 36, generator=g).to(torch.bfloat16).cuda()
+    ids = i32([3, 49, 0, 17])
+    x = torch.empty(4, 36, dtype=torch.float32).cuda()
+    K.embed_gather_scaled(table, ids, x, 2.5)
+    H.assert_close(x.cpu().numpy(), table.float().cpu().numpy()[[3, 49, 0, 17]] * 2.5, 1e-7, "scaled rows")
+    z = torch.randn(4, 5, generator=g).cuda() * 2
+    out = torch.empty(4, 5, dtype=torch.float32).cuda()
+    K.gelu_times_table(z, table, 30, ids, out)
+    want = pr.gelu_tanh(z.double().cpu().numpy()) * table.double().cpu().numpy()[[3, 49, 0, 17]][:, 30:35]
+    H.assert_close(out.cpu().numpy(), want, 2e-6, "gelu(z) * columns of the token's row")
+    v = (torch.randn(3, 11, generator=g) * 40).cuda()
+    want = 15.0 * np.tanh(v.double().cpu().numpy() / 15.0)
+    K.softcap(v, 15.0)
+    H.assert_close(v.cpu().numpy(), want, 2e-6, "soft cap")
+
+
+def _state_group(shape, slots):
+    from aien_sovereign_core_mv_b200.parts import GroupView
+    st = torch.full((2, slots + 1) + tuple(shape), 7.5, dtype=torch.float32).cuda()      # what a slot held before must not matter
+    return st, lambda slot_list: GroupView("state", 16, 0, 0, None, i32(slot_list), {"state": st})
+
+
+@pytest.mark.parametrize("heads,dim,vdim,decay", [(3, 20, 12, [0.5, 0.9, 1.0]), (2, 64, 70, [0.0, 0.999]), (1, 130, 8, [0.97])])
+def test_decayed_linear_attention_in_one_step_and_in_pieces(heads, dim, vdim, decay):
+    """Two requests of unequal length in one step against the token-by-token recurrence; then the same tokens in pieces
+    (33, 1, 1, 2, the rest: across the kernel's chunk of 32) through a slot that another request used before."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(dim)
+    D, eps = 48, 1e-5
+    lens = [77, 5]
+    T = sum(lens)
+    p = {n: (torch.randn(r, D, generator=g) / math.sqrt(D)).double().numpy() for n, r in
+         (("q", heads * dim), ("k", heads * dim), ("v", heads * vdim), ("g", heads * vdim))}
+    h = torch.randn(T, D, generator=g).double().numpy()
+    proj = torch.tensor(np.concatenate([h @ p["q"].T, h @ p["k"].T, h @ p["v"].T, h @ p["g"].T], axis=1), dtype=torch.float32).cuda()
+    dec = torch.tensor(decay, dtype=torch.float32).cuda()
+    st, _ = _state_group((heads, dim, vdim), 3)
+
+    def plain(rows, state=None):
+        T_ = rows.shape[0]
+        q, k, v = (pr.silu(rows @ p[n].T) for n in ("q", "k", "v"))
+        q, k, v = q.reshape(T_, heads, dim), k.reshape(T_, heads, dim), v.reshape(T_, heads, vdim)
+        S = np.zeros((heads, dim, vdim)) if state is None else state.copy()
+        o = np.zeros((T_, heads, vdim))
+        for t in range(T_):
+            for hd in range(heads):
+                S[hd] = decay[hd] * S[hd] + np.outer(k[t, hd], v[t, hd])
+                o[t, hd] = S[hd].T @ q[t, hd]
+        return o.reshape(T_, heads * vdim), S
+
+    want0, S0 = plain(h[:lens[0]])
+    want1, S1 = plain(h[lens[0]:])
+    out = torch.zeros(T, heads * vdim, dtype=torch.float32).cuda()
+    K.decay_linear_attention(proj, 0, heads * dim, 2 * heads * dim, dec, st[1], i32([2, 0]), i32([0, lens[0], T]),
+                             i32(list(range(lens[0])) + list(range(lens[1]))), out, 2, heads, dim, vdim)
+    H.assert_close(out.cpu().numpy(), np.concatenate([want0, want1]), 2e-5, "two requests in one step")
+    H.assert_close(st[1, 2].cpu().numpy(), S0, 2e-5, "state of the first")
+    H.assert_close(st[1, 0].cpu().numpy(), S1, 2e-5, "state of the second")
+    assert float((st[0] - 7.5).abs().max()) == 0.0 and float((st[1, 1] - 7.5).abs().max()) == 0.0     # other runs and slots untouched
+    # the first request again, in pieces, through slot 0 (which holds the second request's state): position 0 starts from zero
+    at, got = 0, []
+    for n in [33, 1, 1, 2, lens[0] - 37]:
+        o = torch.zeros(n, heads * vdim, dtype=torch.float32).cuda()
+        K.decay_linear_attention(proj[at:at + n], 0, heads * dim, 2 * heads * dim, dec, st[1], i32([0]), i32([0, n]),
+                                 i32(list(range(at, at + n))), o, 1, heads, dim, vdim)
+        got.append(o.cpu().numpy())
+        at += n
+    H.assert_close(np.concatenate(got), want0, 2e-5, "the same tokens in pieces")
+    H.assert_close(st[1, 0].cpu().numpy(), S0, 2e-5, "state after the pieces")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [72, 300])
+def test_gated_recurrence_in_one_step_and_in_pieces(dtype, width):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(width)
+    lens = [41, 6]
+    T = sum(lens)
+    proj = (torch.randn(T, 3 * width, generator=g) * 2).cuda()
+    bz, bx = torch.randn(width, generator=g).cuda(), torch.randn(width, generator=g).cuda()
+    st, _ = _state_group((width,), 2)
+    pz, px, pg = (proj[:, i * width:(i + 1) * width].double().cpu().numpy() for i in range(3))
+
+    def plain(lo, hi, S=None):
+        z = pr.sigmoid(pz[lo:hi] + bz.double().cpu().numpy())
+        u = px[lo:hi] + bx.double().cpu().numpy()
+        cand = np.where(u >= 0, u + 0.5, pr.sigmoid(u))
+        S = np.zeros(width) if S is None else S.copy()
+        o = np.zeros((hi - lo, width))
+        for t in range(hi - lo):
+            S = (1 - z[t]) * S + z[t] * cand[t]
+            o[t] = S
+        return o * pr.silu(pg[lo:hi]), S
+
+    want0, S0 = plain(0, lens[0])
+    want1, S1 = plain(lens[0], T)
+    tol = 2e-5 if dtype == torch.float32 else 8e-3
+    out = torch.zeros(T, width, dtype=dtype).cuda()
+    K.gated_recurrence(proj, 0, width, 2 * width, bz, bx, st[0], i32([1, 0]), i32([0, lens[0], T]),
+                       i32(list(range(lens[0])) + list(range(lens[1]))), out, 2, width)
+    H.assert_close(out.float().cpu().numpy(), np.concatenate([want0, want1]), tol, "two requests in one step")
+    H.assert_close(st[0, 1].cpu().numpy(), S0, 2e-5, "state of the first")
+    at, got = 0, []
+    for n in [3, 1, 2, 5, lens[0] - 11]:
+        o = torch.zeros(n, width, dtype=dtype).cuda()
+        K.gated_recurrence(proj[at:at + n], 0, width, 2 * width, bz, bx, st[0], i32([0]), i32([0, n]), i32(list(range(at, at + n))), o, 1, width)
+        got.append(o.float().cpu().numpy())
+        at += n
+    H.assert_close(np.concatenate(got), want0, tol, "the same tokens in pieces, through a slot used before")
+    H.assert_close(st[0, 0].cpu().numpy(), S0, 2e-5, "state after the pieces")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("q_rank,kv_rank,rot_dim", [(48, 40, 8), (16, 96, 16), (130, 64, 0)])
+def test_latents_norms_rotation_and_cache_rows(dtype, q_rank, kv_rank, rot_dim):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(q_rank)
+    T, eps, base = 6, 1e-5, 777.0
+    pos = [0, 1, 17, 64, 1000, 70001]
+    d = torch.randn(T, q_rank + kv_rank + rot_dim, generator=g).cuda()
+    wq = (torch.rand(q_rank, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda()
+    wkv = (torch.rand(kv_rank, generator=g) * 0.4 + 0.8).to(torch.bfloat16).cuda()
+    cos = sin = None
+    if rot_dim:
+        ang = np.asarray(pos, dtype=np.float64)[:, None] * np.array([base ** (-2.0 * i / rot_dim) for i in range(rot_dim // 2)])[None]
+        cos, sin = torch.tensor(np.cos(ang), dtype=torch.float32).cuda(), torch.tensor(np.sin(ang), dtype=torch.float32).cuda()
+    slots = i32([3, 9, 0, -1, 5, 8])
+    cache = torch.zeros(12, kv_rank + rot_dim, dtype=dtype).cuda()
+    cq = torch.empty(T, q_rank, dtype=dtype).cuda()
+    K.latent_prepare(d, q_rank, wq, eps, cq, q_rank, kv_rank, rot_dim, rot_dim, wkv, cos, sin, slots, cache)
+    dn = d.double().cpu().numpy()
+    tol = 3e-6 if dtype == torch.float32 else 8e-3
+    H.assert_close(cq.float().cpu().numpy(), pr.rms_norm(dn[:, :q_rank], wq.double().cpu().numpy(), eps), tol, "query latent")
+    c = pr.rms_norm(dn[:, q_rank:q_rank + kv_rank], wkv.double().cpu().numpy(), eps)
+    kr = pr.rotate_pairs(dn[:, q_rank + kv_rank:], pos, base, rot_dim) if rot_dim else dn[:, q_rank + kv_rank:]
+    for t, s in enumerate(slots.tolist()):
+        if s >= 0:
+            H.assert_close(cache[s].float().cpu().numpy(), np.concatenate([c[t], kr[t]]), tol, f"cache row of token {t}")
+    used = [s for s in slots.tolist() if s >= 0]
+    assert all(float(cache[s].abs().max()) == 0.0 for s in range(12) if s not in used)     # a token without a slot writes nothing
+    if rot_dim:                                                       # the query's rotated part, moved behind its latent
+        heads, dim = 3, 10
+        q = torch.randn(T, heads * (dim + rot_dim), generator=g).cuda()
+        qf = torch.zeros(T, heads * (kv_rank + rot_dim), dtype=torch.float32).cuda()
+        K.rotate_pairs_rows(q, dim + rot_dim, dim, qf, kv_rank + rot_dim, kv_rank, heads, rot_dim, rot_dim, cos, sin)
+        qh = q.double().cpu().numpy().reshape(T, heads, dim + rot_dim)
+        H.assert_close(qf.cpu().numpy().reshape(T, heads, -1)[:, :, kv_rank:], pr.rotate_pairs(qh[:, :, dim:], pos, base, rot_dim), 3e-6, "rotated query part")
+        assert float(qf.reshape(T, heads, -1)[:, :, :kv_rank].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,n,k", [(5, 40, 24), (17, 128, 64), (1, 7, 3)])
+def test_one_product_per_head(dtype, heads, n, k):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(n)
+    T = 9
+    a = torch.randn(T, heads * (k + 4), generator=g).to(dtype).cuda()                # four numbers of something else behind every head
+    w = (torch.randn(heads, n, k, generator=g) / math.sqrt(k)).to(dtype).cuda()
+    out = torch.zeros(T, heads * (n + 2) + 1, dtype=torch.float32).cuda()
+    K.head_project(a, k + 4, 0, w, out, n + 2, 1)
+    ah = a.double().cpu().numpy().reshape(T, heads, k + 4)[:, :, :k]
+    want = np.einsum("thk,hnk->thn", ah, w.double().cpu().numpy())
+    got = out.cpu().numpy()[:, 1:].reshape(T, heads, n + 2)
+    H.assert_close(got[:, :, :n], want, 2e-6, "products")
+    assert float(np.abs(got[:, :, n:]).max()) == 0.0 and float(out[:, 0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,page,heads,r,rd", [(21, 16, 5, 40, 8), (64, 16, 17, 128, 32), (0, 8, 1, 96, 16), (16, 16, 4, 64, 64), (7, 32, 3, 520, 0)])
+def test_latent_attention_sees_its_window_and_the_sink(dtype, window, page, heads, r, rd):
+    """Queries at several positions of a request of 150 tokens whose pages lie scattered.  The keys just inside the
+    window (distance window - 1), just outside (distance window), at position 0 and on both sides of a page border are
+    scaled so that each would take nearly all the weight if it were seen; one head's sink is made large."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(window + r)
+    n, D, scale = 150, r + rd, 0.2
+    rows = torch.randn(n, D, generator=g) * 0.5
+    qpos = [0, 1, page - 1, page, 2 * page, 99, 100, 149]
+    loud = {p - far for p in qpos for far in ([window - 1, window] if window else [p]) if p - far >= 0}
+    for j in sorted(loud):
+        rows[j] *= 3.0
+    rows = rows.to(dtype)
+    order = list(np.random.default_rng(3).permutation((n + page - 1) // page + 3))
+    cache = torch.zeros((max(order) + 1) * page, D, dtype=dtype)
+    for j in range(n):
+        cache[order[j // page] * page + j % page] = rows[j]
+    bt = torch.full((2, 64), -1, dtype=torch.int32)
+    bt[1, :(n + page - 1) // page] = torch.tensor(order[:(n + page - 1) // page], dtype=torch.int32)
+    q = torch.randn(len(qpos), heads * D, generator=g) * 0.7
+    sinks = torch.randn(heads, generator=g)
+    sinks[0] = 6.0
+    out = torch.zeros(len(qpos), heads * r, dtype=dtype).cuda()
+    K.latent_attention(q.cuda(), cache.cuda(), bt.cuda(), 64, i32([1] * len(qpos)), i32(qpos), out, heads, r, rd, page, window, scale, sinks.cuda())
+    rn, qn = rows.double().numpy(), q.double().numpy().reshape(len(qpos), heads, D)
+    want = np.zeros((len(qpos), heads, r))
+    for t, p in enumerate(qpos):
+        seen = [j for j in range(n) if j <= p and (window == 0 or p - j < window)]
+        for hd in range(heads):
+            s = np.array([qn[t, hd] @ rn[j] * scale for j in seen])
+            m = max(s.max(), float(sinks[hd]))
+            e = np.exp(s - m)
+            want[t, hd] = (e[:, None] * rn[seen][:, :r]).sum(0) / (e.sum() + math.exp(float(sinks[hd]) - m))
+    H.assert_close(out.float().cpu().numpy().reshape(len(qpos), heads, r), want, 1e-5 if dtype == torch.float32 else 1e-2, "weighted latents")
+
+
+# ------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_layers_of_a_short_request_float32(models, which):
+    """The stream after every layer, so that a fault names its layer."""
+    d, reqs, _ = models[which]
+    cfg, tensors = load_plain(d)
+    toks = reqs[2]
+    want = []
+    pr.forward(cfg, tensors, toks, want)
+    eng = H.engine_for(d, "float32", PAGE[which], 256, replay_steps=False)
+    seen = []
+    for b in eng.model.blocks:
+        def wrapped(ctx, x, delta, run, next_norm=None, _inner=b.forward):
+            out = _inner(ctx, x, delta, run, next_norm=next_norm)
+            seen.append(x.clone())
+            return out
+        b.forward = wrapped
+    eng.step([(1, toks, [0])])
+    assert len(seen) == len(want)
+    for i, (a, w) in enumerate(zip(seen, want)):
+        H.assert_close(a.cpu().numpy(), w, 2e-5, f"{which}: stream after layer {i} ({cfg['layers'][i]['type']})")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_whole_requests(models, which, dtype, tol):
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    steps = [([(rid, toks, list(range(len(toks))))], [rid]) for rid, toks in reqs.items()]
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} whole")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_prefill_then_token_by_token(models, which, dtype, tol):
+    """Most of the longest request in one step, then 40 tokens one by one: the decoded tokens' windows pass over the
+    prompt's end, and pages behind a window are given back while the request runs."""
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    toks = reqs[rid]
+    cut = len(toks) - 40
+    steps = [([(rid, toks[:cut], [0, cut - 1])], [])] + [([(rid, [toks[i]], [0])], []) for i in range(cut, len(toks))]
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} decode")
+    state = eng.cache_state()
+    assert state["check"] == "" and (which == "B" or state["metrics"]["window_releases"] > 0)
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_first_tokens_one_by_one(models, which, dtype, tol):
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    steps = [([(rid, [t], [0])], []) for t in reqs[rid][:45]]
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} from the first token")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_changing_portions(models, which, dtype, tol):
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    sizes = [7, 2, 13, 3, 2, 29, 5, 2, 16, 17, 1, 8, 64, 2, 31]
+    for rid, toks in reqs.items():
+        steps, at, k = [], 0, rid
+        while at < len(toks):
+            n = min(sizes[k % len(sizes)], len(toks) - at)
+            steps.append(([(rid, toks[at:at + n], list(range(n)))], []))
+            at += n
+            k += 1
+        steps[-1] = (steps[-1][0], [rid])
+        check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} portions of request {rid}")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_mixed_batches_on_few_pages_and_slots(models, which, dtype, tol):
+    """Unequal requests side by side, portions beside single tokens, with three state slots and a pool so small that
+    pages and slots are used again; every logit equals the request's alone."""
+    d, reqs, want = models[which]
+    page = PAGE[which]
+    reqs = dict(reqs)
+    reqs.update({rid + 10: toks[: max(1, len(toks) - 3)] for rid, toks in list(reqs.items())})          # more requests than slots
+    want = dict(want)
+    want.update({rid: want[rid - 10] for rid in reqs if rid > 10})
+    longest = max(len(t) for t in reqs.values())
+    pool = ((longest + page - 1) // page + 6) * page
+    if which == "B":                                               # no mask: every key stays, so the three live requests must fit whole
+        pool = (3 * ((longest + page - 1) // page + 1) + 2) * page
+    eng = H.engine_for(d, dtype, page, pool, max_requests=3)
+    rng = np.random.default_rng(5)
+    at = {rid: 0 for rid in reqs}
+    waiting, live, steps = sorted(reqs, key=lambda r: (len(reqs[r]), r)), [], []
+    held = lambda: sum((at[r] + page - 1) // page + 1 for r in live)
+    while waiting or live:
+        while waiting and len(live) < 3 and (held() + (len(reqs[waiting[0]]) + page - 1) // page + 2) * page <= pool:
+            live.append(waiting.pop(0))
+        if not live:
+            live.append(waiting.pop(0))
+        entries, end = [], []
+        for rid in list(live):
+            left = len(reqs[rid]) - at[rid]
+            n = 1 if rng.random() < 0.4 else int(min(left, rng.integers(2, 40)))
+            n = min(n, left)
+            if rng.random() < 0.15 and len(live) > 1:
+                continue                                            # a request may sit a step out
+            entries.append((rid, reqs[rid][at[rid]:at[rid] + n], list(range(n))))
+            at[rid] += n
+            if at[rid] == len(reqs[rid]):
+                end.append(rid)
+                live.remove(rid)
+        if entries:
+            steps.append((entries, end))
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} mixed")
+    state = eng.cache_state()
+    assert state["check"] == "" and state["requests"] == 0
+
+
+def test_a_window_gives_pages_back_and_takes_them_again(models):
+    """A request longer than the pool runs, because only its window is held; a second request then reuses the pages."""
+    d, reqs, want = models["A"]                                     # windows of 21 and 9 positions on one cache, pages of 16
+    eng = H.engine_for(d, "float32", 16, 6 * 16, max_requests=2, max_batch_tokens=64)
+    toks = reqs[4]                                                  # 131 tokens through a pool of 96
+    steps, at = [], 0
+    for n in [30, 2, 17, 1, 1, 40, 9, 31]:
+        steps.append(([(4, toks[at:at + n], list(range(n)))], []))
+        at += n
+    assert at == len(toks)
+    steps[-1] = (steps[-1][0], [4])
+    steps.append(([(3, reqs[3], list(range(len(reqs[3]))))], [3]))
+    check(H.run_steps(eng, steps), want, FP32_TOL, "A float32 through a pool smaller than the request")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["metrics"]["window_releases"] >= 3
+
+
+def test_long_decoding_bfloat16_graphs(models):
+    """130 decode-only steps of two requests (captured graphs, state slots and windows moving on): along the given tokens
+    the logits stay with the plain implementation."""
+    d, reqs, want = models["C"]
+    eng = H.engine_for(d, "bfloat16", 16, 1024)
+    a, b = reqs[3], reqs[2]
+    steps = [([(3, a[:15], [14]), (2, b[:4], [3])], [])]
+    for i in range(min(len(a) - 15, len(b) - 4)):
+        steps.append(([(3, [a[15 + i]], [0]), (2, [b[4 + i]], [0])], []))
+    check(H.run_steps(eng, steps), want, BF16_TOL, "C bfloat16 long decoding")
+    assert len(eng._graphs) > 0                                     # the decode-only steps ran as captured graphs
+
+
+def test_greedy_generation_through_the_entry_point(models):
+    from aien_sovereign_core_mv_b200.engine.generate import generate
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d, reqs, _ = models["A"]
+    cfg, tensors = load_plain(d)
+    prompts = [reqs[2], reqs[3][:30], reqs[1]]
+    n_new = 10
+    want = []
+    for p in prompts:
+        seq, out = list(p), []
+        for _ in range(n_new):
+            t = int(np.argmax(pr.forward(cfg, tensors, seq)[-1]))
+            seq.append(t); out.append(t)
+        want.append(out)
+    eng = H.engine_for(d, "float32", 16, 512, prefill_chunk_size=16, max_prefill_tokens=32)
+    got = generate(eng, prompts, SamplingParams(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    assert got == want
+    assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
+
+
+def test_sampling_and_the_command_line(models):
+    import subprocess
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d, reqs, _ = models["B"]
+    eng = H.engine_for(d, "bfloat16", 8, 512)
+    params = SamplingParams(temperature=0.8, top_p=0.9, top_k=40, max_tokens=12, stop_token_ids=[], seed=7)
+    a = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
+    b = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
+    assert [r.tokens for r in a] == [r.tokens for r in b] and all(len(r.tokens) == 12 for r in a)
+    exe = os.path.join(H.ROOT, "bin", "aien-b200")
+    info = subprocess.run([exe, "info", "--model-dir", d], capture_output=True, text=True, timeout=600)
+    assert info.returncode == 0, info.stderr[-2000:]
+    rec = json.loads(info.stdout.strip().splitlines()[-1])
+    assert rec["architecture"] == "Ripesun" and rec["layers"] == 3 and sorted(rec["cache_groups"]) == ["full", "state"]
+
+
+def test_trace_replay_from_the_command(models, tmp_path):
+    d, reqs, want = models["A"]
+    toks = reqs[3]
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:40], "want": [0, 39]}, {"id": 7, "tokens": reqs[1], "want": [0]}], "end": [7]},
+             {"step": 1, "entries": [{"id": "x", "tokens": toks[40:42], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": toks[42:], "want": [len(toks) - 43]}], "end": ["x"]}]
+    out = H.run_trace(d, "float32", str(tmp_path / "out"), 192, steps)
+    assert sorted(out) == [0, 2]
+    H.assert_close(out[0], np.stack([want[3][0], want[3][39], want[1][0]]), FP32_TOL, "trace step 0")
+    H.assert_close(out[2], want[3][-1:], FP32_TOL, "trace step 2")
