@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step|dulisun]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step|dulisun|ripesun]
 
 A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
 limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
@@ -360,6 +360,114 @@ def dulisun_workload(only: str = "") -> int:
     return 0
 
 
+def _ripesun_config(width, heads, dim, vdim, rot, kv_rank, q_rank, window, gru, ff, side, layers, vocab):
+    light = {"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": vdim,
+                                            "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, heads - 1)) for h in range(heads)]},
+             "mlp": {"kind": "dense", "ff": ff}}
+    gru_layer = {"type": "mingru", "mixer": {"width": gru}, "mlp": {"kind": "dense", "ff": ff}}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "scale": (dim + rot) ** -0.5,
+              "rot": {"base": 10000.0, "dims": rot}, "mask": {"size": window}}
+    pattern, out = ("lightning", "mingru", "latent", "lightning", "mingru", "shared"), []
+    first_latent = None
+    for i in range(layers):
+        kind = pattern[i % len(pattern)]
+        if kind == "lightning":
+            out.append(light)
+        elif kind == "mingru":
+            out.append(gru_layer)
+        elif kind == "latent" or first_latent is None:
+            first_latent = i if first_latent is None else first_latent
+            out.append({"type": "latent_attention", "mixer": dict(latent), "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            out.append({"type": "latent_attention", "mixer": dict(latent, kv_from=first_latent), "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Ripesun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "residual_mult": 0.5, "logit_softcap": 30.0, "token_side": {"dim": side}, "layers": out}
+
+
+# (name, Ripesun sizes); layers follow the pattern lightning, mingru, latent attention, lightning, mingru, latent attention
+# reading the first one's cache.  The dense model beside each has the same width, heads, head size, layers and vocabulary,
+# grouped-query attention with a quarter of the heads as key/value heads, and an intermediate size that gives a token the
+# same feed-forward arithmetic: 3 * I = 2 * ff, rounded to a multiple of 256.
+RIPESUN_SHAPES = (
+    ("w2048_h16", dict(width=2048, heads=16, dim=128, vdim=128, rot=64, kv_rank=512, q_rank=1536, window=1024, gru=2048, ff=6144,
+                       side=128, layers=6, vocab=32768)),
+    ("w4096_h32", dict(width=4096, heads=32, dim=128, vdim=128, rot=64, kv_rank=512, q_rank=1536, window=2048, gru=4096, ff=12288,
+                       side=256, layers=3, vocab=32768)),
+    ("w1024_h16", dict(width=1024, heads=16, dim=64, vdim=64, rot=32, kv_rank=256, q_rank=512, window=256, gru=1024, ff=3072,
+                       side=64, layers=6, vocab=32768)),
+)
+
+
+def ripesun_workload(only: str = "") -> int:
+    """Prefill and decode throughput of the Ripesun design at a few sizes that resemble a real model's layers (random
+    bfloat16 weights), each beside the dense Qwen3-style model of equal width, heads, layers, vocabulary and per-token
+    feed-forward arithmetic.  Prefill: one prompt of 2,048 tokens; decode: 8 and 64 requests at 1,024 tokens of context,
+    captured graphs.  Timed on the device with CUDA events after warm-up; every step reads more weights than L2 holds.
+    The timed steps lie between cudaProfilerStart and cudaProfilerStop."""
+    import torch
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200 import kernels as K
+    results = []
+    P, CTX = 2048, 1024
+    for name, sz in RIPESUN_SHAPES:
+        if only and only != name:
+            continue
+        inter = int(round(2 * sz["ff"] / 3 / 256)) * 256
+        dense = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=sz["layers"], hidden_size=sz["width"],
+                     num_attention_heads=sz["heads"], num_key_value_heads=max(1, sz["heads"] // 4), head_dim=sz["dim"], intermediate_size=inter,
+                     vocab_size=sz["vocab"], rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                     max_position_embeddings=8192, hidden_act="silu", attention_bias=False, eos_token_id=0)
+        row = {"shape": name, "sizes": dict(sz), "dense_intermediate": inter}
+        for which, cfg in (("ripesun", _ripesun_config(**sz)), ("dense", dense)):
+            ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=64 * (CTX + 64) + P + 64, max_requests=64,
+                              max_batch_tokens=P, max_context=4096, max_batch_size=64)
+            eng = Engine.from_config(cfg, seed=5, engine_config=ec, init_std=0.02, device_init=True)
+            V = sz["vocab"]
+            toks = lambda n, s: [(7 * i + 13 * s) % V for i in range(n)]
+
+            def timed(fn, warm, reps):
+                for i in range(warm):
+                    fn(i)
+                torch.cuda.synchronize()
+                ms = []
+                for i in range(reps):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn(warm + i)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms.append(e0.elapsed_time(e1))
+                return sorted(ms)[len(ms) // 2]
+
+            def prefill(i):
+                eng.step([(9000 + i, toks(P, i), [P - 1])])
+                eng.end_request(9000 + i)
+
+            out = {}
+            torch.cuda.profiler.start()
+            t = timed(prefill, 3, 5)
+            out["prefill_2048"] = {"ms": round(t, 3), "tokens_per_s": round(P / t * 1e3, 1)}
+            for batch in (8, 64):
+                for r in range(0, batch, 2):
+                    eng.step([(r, toks(CTX, r), []), (r + 1, toks(CTX, r + 1), [])])
+                t = timed(lambda i: eng.step([(r, [(i + r) % V], [0]) for r in range(batch)]), 4, 12)
+                out[f"decode_b{batch}"] = {"ms": round(t, 3), "tokens_per_s": round(batch / t * 1e3, 1)}
+                for r in range(batch):
+                    eng.end_request(r)
+            torch.cuda.profiler.stop()
+            eng.check_waits()
+            out["wait_errors"] = sum(1 for w in K.read_wait_errors() if w != 0)
+            row[which] = out
+            del eng
+            torch.cuda.empty_cache()
+        results.append(row)
+    print(json.dumps({"metric": "ripesun_beside_dense", "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+                      "data": "synthetic", "impl": "ours", "shapes": results,
+                      "config": {"prefill_tokens": P, "decode_context": CTX, "page_size": 16, "seed": 5,
+                                 "l2": "weights read per step exceed L2"}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,16 +486,17 @@ def main() -> int:
     ap.add_argument("--top-k", type=int, default=0, help="top-k of the end-to-end run")
     ap.add_argument("--align-step-tokens", type=int, default=0,
                     help="serving workload: the scheduler cuts portions so that a step's tokens fill whole tiles of this many rows")
-    ap.add_argument("--shape", default="", help="dulisun workload: only this shape (default: all)")
+    ap.add_argument("--shape", default="", help="dulisun and ripesun workloads: only this shape (default: all)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step", "dulisun"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step", "dulisun", "ripesun"],
                     help="decode: the headline decode-step measurement (Qwen3-8B shape, 1,024-token prompts); llama3_8b: the same "
                          "line for the Llama-3-8B shape, 16 requests at contexts ending at 8,192 tokens; serving: continuous batching "
                          "of 32 requests on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each); "
                          "mixed_step: one step of a 512-token portion beside 24 decoding requests on that shape, timed alone; "
-                         "dulisun: prefill and decode of the Dulisun design at a few sizes beside the dense model of equal size")
+                         "dulisun: prefill and decode of the Dulisun design at a few sizes beside the dense model of equal size; "
+                         "ripesun: the same for the Ripesun design")
     ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
                     help="how requests get their prompt: real prefill, or (development only) cache pages "
                          "filled with random keys/values without running the model")
@@ -407,6 +516,8 @@ def main() -> int:
         return mixed_step_workload()
     if args.workload == "dulisun":
         return dulisun_workload(args.shape)
+    if args.workload == "ripesun":
+        return ripesun_workload(args.shape)
 
     import numpy as np
     import torch
