@@ -112,6 +112,217 @@ decay_linear_attention_kernel(const TP* __restrict__ proj, long ld, int q_off, i
     }
 }
 
+// ---------------------------------------------------------------- the same, chunks side by side
+// For portions of prompts the chunks of a request need not wait for one another.  Three launches:
+//   1. every chunk's own contribution to the state   U_c = sum_j lambda^(n-1-j) k_j v_j^T        (chunks in parallel)
+//   2. per request, over its chunks in order          P_c = S (the state before chunk c); S = lambda^n S + U_c
+//      (element by element; P_c overwrites U_c in place; the request's slot gets the last S)
+//   3. every chunk's outputs                          o_i = sum_{j<=i} (q_i . k_j) lambda^(i-j) v_j + lambda^(i+1) P_c^T q_i
+// Chunks of LC tokens are counted from the start of each request's portion; the step has at most T / LC + S of them,
+// and a CTA finds its request and chunk from q_start.  All products are float32 on the CUDA cores, in register tiles
+// fed from shared memory; a step's result differs from the token-by-token recurrence by rounding only.
+constexpr int LC = 64, LVT = 64, LDT = 128, LPAD = 68;
+
+__device__ __forceinline__ bool la_locate(const int* __restrict__ q_start, int S, int c, int& s_out, int& t0, int& n) {
+    int acc = 0;
+    for (int s = 0; s < S; ++s) {
+        const int len = q_start[s + 1] - q_start[s];
+        const int nch = (len + LC - 1) / LC;
+        if (c < acc + nch) {
+            const int k = c - acc;
+            s_out = s;
+            t0 = q_start[s] + k * LC;
+            n = min(LC, len - k * LC);
+            return true;
+        }
+        acc += nch;
+    }
+    return false;
+}
+
+template <typename TP>
+__global__ void __launch_bounds__(256)
+la_chunk_state_kernel(const TP* __restrict__ proj, long ld, int k_off, int v_off, const float* __restrict__ decay,
+                      const int* __restrict__ q_start, int S, float* __restrict__ U, int H, int dim, int vd) {
+    __shared__ __align__(16) float Ks[LC][LDT];
+    __shared__ __align__(16) float Vs[LC][LVT];
+    int s, t0, n;
+    const int c = blockIdx.x, h = blockIdx.y;
+    if (!la_locate(q_start, S, c, s, t0, n)) return;
+    const int vtiles = (vd + LVT - 1) / LVT;
+    const int d0 = (blockIdx.z / vtiles) * LDT, v0 = (blockIdx.z % vtiles) * LVT;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float l2 = log2f(decay[h]);
+    for (int idx = tid; idx < n * LDT; idx += 256) {
+        const int j = idx / LDT, d = idx % LDT;
+        float v = 0.f;
+        if (d0 + d < dim) v = silu_f(to_f(proj[(size_t)(t0 + j) * ld + k_off + (size_t)h * dim + d0 + d])) * decay_pow(l2, n - 1 - j);
+        Ks[j][d] = v;
+    }
+    for (int idx = tid; idx < n * LVT; idx += 256) {
+        const int j = idx / LVT, v = idx % LVT;
+        Vs[j][v] = (v0 + v < vd) ? silu_f(to_f(proj[(size_t)(t0 + j) * ld + v_off + (size_t)h * vd + v0 + v])) : 0.f;
+    }
+    __syncthreads();
+    float acc[8][4];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int j = 0; j < n; ++j) {
+        const float4 ka = *reinterpret_cast<const float4*>(&Ks[j][ty * 8]);
+        const float4 kb = *reinterpret_cast<const float4*>(&Ks[j][ty * 8 + 4]);
+        const float4 vv = *reinterpret_cast<const float4*>(&Vs[j][tx * 4]);
+        const float k8[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+        const float v4[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(k8[a], v4[b], acc[a][b]);
+    }
+    float* u = U + ((size_t)c * H + h) * dim * vd;
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+        const int d = d0 + ty * 8 + a;
+        if (d >= dim) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int v = v0 + tx * 4 + b;
+            if (v < vd) u[(size_t)d * vd + v] = acc[a][b];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+la_state_scan_kernel(float* __restrict__ U, const float* __restrict__ decay, float* __restrict__ state,
+                     const int* __restrict__ slot_map, const int* __restrict__ q_start, const int* __restrict__ positions,
+                     int H, int dim, int vd) {
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int e = blockIdx.x * 256 + threadIdx.x;
+    const int E = dim * vd;
+    if (e >= E) return;
+    int base = 0;
+    for (int r = 0; r < s; ++r) base += (q_start[r + 1] - q_start[r] + LC - 1) / LC;
+    const int t0 = q_start[s], len = q_start[s + 1] - t0;
+    if (len <= 0) return;
+    float* st = state + ((size_t)slot_map[s] * H + h) * E + e;
+    float Sv = positions[t0] == 0 ? 0.f : *st;
+    const float l2 = log2f(decay[h]);
+    const float full = decay_pow(l2, LC);
+    const int nch = (len + LC - 1) / LC;
+    for (int k = 0; k < nch; ++k) {
+        float* u = U + ((size_t)(base + k) * H + h) * E + e;
+        const float uv = *u;
+        *u = Sv;
+        const int n = min(LC, len - k * LC);
+        Sv = fmaf(n == LC ? full : decay_pow(l2, n), Sv, uv);
+    }
+    *st = Sv;
+}
+
+template <typename TP>
+__global__ void __launch_bounds__(256)
+la_chunk_output_kernel(const TP* __restrict__ proj, long ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                       const int* __restrict__ q_start, int S, const float* __restrict__ P, float* __restrict__ out, long ldo,
+                       int H, int dim, int vd) {
+    extern __shared__ __align__(16) float sm[];
+    float* Qt = sm;                         // [dim][LPAD]: Qt[d][i]
+    float* Kt = Qt + (size_t)dim * LPAD;    // [dim][LPAD]
+    float* At = Kt + (size_t)dim * LPAD;    // [LC][LPAD]: At[j][i]
+    float* Vs = At + LC * LPAD;             // [LC][LVT]
+    int s, t0, n;
+    const int c = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LVT;
+    if (!la_locate(q_start, S, c, s, t0, n)) return;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float l2 = log2f(decay[h]);
+    for (int idx = tid; idx < LC * dim; idx += 256) {
+        const int j = idx / dim, d = idx % dim;
+        float qv = 0.f, kv = 0.f;
+        if (j < n) {
+            const TP* row = proj + (size_t)(t0 + j) * ld + (size_t)h * dim + d;
+            qv = silu_f(to_f(row[q_off]));
+            kv = silu_f(to_f(row[k_off]));
+        }
+        Qt[d * LPAD + j] = qv;
+        Kt[d * LPAD + j] = kv;
+    }
+    for (int idx = tid; idx < LC * LVT; idx += 256) {
+        const int j = idx / LVT, v = idx % LVT;
+        Vs[idx] = (j < n && v0 + v < vd) ? silu_f(to_f(proj[(size_t)(t0 + j) * ld + v_off + (size_t)h * vd + v0 + v])) : 0.f;
+    }
+    __syncthreads();
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    // scores of the chunk: rows i = ty*4.., keys j = tx*4..; tiles wholly above the diagonal stay zero
+    if (tx <= ty) {
+        for (int d = 0; d < dim; ++d) {
+            const float4 qq = *reinterpret_cast<const float4*>(&Qt[d * LPAD + ty * 4]);
+            const float4 kk = *reinterpret_cast<const float4*>(&Kt[d * LPAD + tx * 4]);
+            const float q4[4] = {qq.x, qq.y, qq.z, qq.w}, k4[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(q4[a], k4[b], acc[a][b]);
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int i = ty * 4 + a, j = tx * 4 + b;
+            At[j * LPAD + i] = (j <= i) ? acc[a][b] * decay_pow(l2, i - j) : 0.f;
+        }
+    __syncthreads();
+    // outputs: rows i = ty*4.., value columns tx*4..
+    float o1[4][4], o2[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) o1[a][b] = o2[a][b] = 0.f;
+    const int jmax = min(n, ty * 4 + 4);
+    for (int j = 0; j < jmax; ++j) {
+        const float4 aa = *reinterpret_cast<const float4*>(&At[j * LPAD + ty * 4]);
+        const float4 vv = *reinterpret_cast<const float4*>(&Vs[j * LVT + tx * 4]);
+        const float a4[4] = {aa.x, aa.y, aa.z, aa.w}, v4[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) o1[a][b] = fmaf(a4[a], v4[b], o1[a][b]);
+    }
+    const float* p = P + ((size_t)c * H + h) * dim * vd + v0 + tx * 4;
+    const bool vec = (vd & 3) == 0 && v0 + tx * 4 + 3 < vd;
+    for (int d = 0; d < dim; ++d) {
+        const float4 qq = *reinterpret_cast<const float4*>(&Qt[d * LPAD + ty * 4]);
+        float p4[4];
+        if (vec) {
+            const float4 pp = *reinterpret_cast<const float4*>(p + (size_t)d * vd);
+            p4[0] = pp.x; p4[1] = pp.y; p4[2] = pp.z; p4[3] = pp.w;
+        } else {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) p4[b] = (v0 + tx * 4 + b < vd) ? p[(size_t)d * vd + b] : 0.f;
+        }
+        const float q4[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) o2[a][b] = fmaf(q4[a], p4[b], o2[a][b]);
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = ty * 4 + a;
+        if (i >= n) continue;
+        const float w = decay_pow(l2, i + 1);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int v = v0 + tx * 4 + b;
+            if (v < vd) out[(size_t)(t0 + i) * ldo + (size_t)h * vd + v] = fmaf(w, o2[a][b], o1[a][b]);
+        }
+    }
+}
+
 // out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * w * sigmoid(g[t]): the norm over all heads together, gated.
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(256)
@@ -179,6 +390,54 @@ gated_recurrence_kernel(const TP* __restrict__ proj, long ld, int z_off, int x_o
     *st = S;
 }
 
+
+// The same recurrence for portions of prompts: the portion is cut into GR_SEG segments that run side by side.  A thread
+// first reduces its segment to (a, b) with S_end = a S_start + b, the segments' pairs are combined in order through
+// shared memory, and the thread walks its segment again from its true starting state, writing the outputs.
+constexpr int GR_SEG = 32;
+
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(32 * GR_SEG)
+gated_recurrence_segments_kernel(const TP* __restrict__ proj, long ld, int z_off, int x_off, int g_off,
+                                 const void* __restrict__ bz, const void* __restrict__ bx, int bdt,
+                                 float* __restrict__ state, const int* __restrict__ slot_map, const int* __restrict__ q_start,
+                                 const int* __restrict__ positions, TO* __restrict__ out, long ldo, int W) {
+    __shared__ float As[GR_SEG][33], Bs[GR_SEG][33];
+    const int s = blockIdx.y, lane = threadIdx.x, seg = threadIdx.y;
+    const int c = blockIdx.x * 32 + lane;
+    const bool live = c < W;
+    const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (t1 <= t0) return;
+    const int per = (t1 - t0 + GR_SEG - 1) / GR_SEG;
+    const int lo = min(t1, t0 + seg * per), hi = min(t1, lo + per);
+    const float bzc = (live && bz) ? load_dyn(bz, bdt, c) : 0.f, bxc = (live && bx) ? load_dyn(bx, bdt, c) : 0.f;
+    float a = 1.f, b = 0.f;
+    if (live) {
+        for (int t = lo; t < hi; ++t) {
+            const TP* row = proj + (size_t)t * ld + c;
+            const float z = sigmoid_f(to_f(row[z_off]) + bzc), u = to_f(row[x_off]) + bxc;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+            b = (1.0f - z) * b + z * cand;
+            a *= (1.0f - z);
+        }
+    }
+    As[seg][lane] = a;
+    Bs[seg][lane] = b;
+    __syncthreads();
+    if (!live) return;
+    float* st = state + (size_t)slot_map[s] * W + c;
+    float Sv = positions[t0] == 0 ? 0.f : *st;
+    for (int k = 0; k < seg; ++k) Sv = As[k][lane] * Sv + Bs[k][lane];
+    for (int t = lo; t < hi; ++t) {
+        const TP* row = proj + (size_t)t * ld + c;
+        const float z = sigmoid_f(to_f(row[z_off]) + bzc), u = to_f(row[x_off]) + bxc;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        Sv = (1.0f - z) * Sv + z * cand;
+        out[(size_t)t * ldo + c] = from_f<TO>(Sv * silu_f(to_f(row[g_off])));
+    }
+    if (hi == t1 && lo < hi) *st = Sv;
+}
+
 }  // namespace aien
 
 using namespace aien;
@@ -217,6 +476,38 @@ AIEN_API int aien_decay_linear_attention(const void* proj, int p_dt, long ld, in
     return launch_status();
 }
 
+template <typename TP>
+static int launch_la_chunked(cudaStream_t stream, const TP* proj, long ld, int q_off, int k_off, int v_off, const float* decay,
+                             float* state, const int* slot_map, const int* q_start, const int* positions, float* out, long ldo,
+                             float* U, int T, int S, int H, int dim, int vd) {
+    const int NC = T / LC + S;
+    const int dtiles = (dim + LDT - 1) / LDT, vtiles = (vd + LVT - 1) / LVT;
+    const size_t smem = ((size_t)2 * dim * LPAD + LC * LPAD + LC * LVT) * sizeof(float);
+    auto kout = la_chunk_output_kernel<TP>;
+    if (smem > 200 * 1024) return AIEN_E_SHAPE;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kout, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return AIEN_E_STATE;
+    la_chunk_state_kernel<TP><<<dim3(NC, H, dtiles * vtiles), 256, 0, stream>>>(proj, ld, k_off, v_off, decay, q_start, S, U, H, dim, vd);
+    la_state_scan_kernel<<<dim3((dim * vd + 255) / 256, H, S), 256, 0, stream>>>(U, decay, state, slot_map, q_start, positions, H, dim, vd);
+    kout<<<dim3(NC, H, vtiles), 256, smem, stream>>>(proj, ld, q_off, k_off, v_off, decay, q_start, S, U, out, ldo, H, dim, vd);
+    return 0;
+}
+
+// The same result as aien_decay_linear_attention for a step of T tokens in S requests, chunks side by side.
+// scratch: float32, (T / 64 + S) * H * dim * vd numbers.
+AIEN_API int aien_decay_linear_attention_chunked(const void* proj, int p_dt, long ld, int q_off, int k_off, int v_off,
+                                                 const float* decay, float* state, const int* slot_map, const int* q_start,
+                                                 const int* positions, float* out, long ldo, float* scratch, int T, int S,
+                                                 int H, int dim, int vd, cudaStream_t stream) {
+    if (S <= 0 || T <= 0) return 0;
+    if (H <= 0 || dim <= 0 || vd <= 0 || H > 65535 || S > 65535 || scratch == nullptr) return AIEN_E_SHAPE;
+    int rc = 0;
+    AIEN_DISPATCH_DTYPE(p_dt, TP, (rc = launch_la_chunked<TP>(stream, (const TP*)proj, ld, q_off, k_off, v_off, decay, state, slot_map,
+                                                              q_start, positions, out, ldo, scratch, T, S, H, dim, vd)));
+    if (rc != 0) return rc;
+    return launch_status();
+}
+
 AIEN_API int aien_gated_rmsnorm(const float* o, long ldo, const void* gate, int g_dt, long ldg, const void* w, int w_dt, float eps,
                                 void* out, int o_dt, long ldout, int T, int N, cudaStream_t stream) {
     if (T <= 0) return 0;
@@ -227,13 +518,19 @@ AIEN_API int aien_gated_rmsnorm(const float* o, long ldo, const void* gate, int 
 }
 
 // proj [T, ld]: z at column z_off, the candidate's input at x_off, the output gate at g_off (W each); bz, bx [W] or null.
-// state float32 [slots, W]; out [T, ldo] in its own dtype.
+// state float32 [slots, W]; out [T, ldo] in its own dtype.  segments != 0: every portion is cut into segments that run side by side.
 AIEN_API int aien_gated_recurrence(const void* proj, int p_dt, long ld, int z_off, int x_off, int g_off,
                                    const void* bz, const void* bx, int b_dt, float* state, const int* slot_map,
                                    const int* q_start, const int* positions, void* out, int o_dt, long ldo,
-                                   int S, int W, cudaStream_t stream) {
+                                   int S, int W, int segments, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (W <= 0 || S > 65535) return AIEN_E_SHAPE;
+    if (segments) {
+        AIEN_DISPATCH_DTYPE(p_dt, TP, AIEN_DISPATCH_DTYPE(o_dt, TO,
+            (gated_recurrence_segments_kernel<TP, TO><<<dim3((W + 31) / 32, S), dim3(32, GR_SEG), 0, stream>>>(
+                (const TP*)proj, ld, z_off, x_off, g_off, bz, bx, b_dt, state, slot_map, q_start, positions, (TO*)out, ldo, W))));
+        return launch_status();
+    }
     dim3 grid((W + 127) / 128, S);
     AIEN_DISPATCH_DTYPE(p_dt, TP, AIEN_DISPATCH_DTYPE(o_dt, TO,
         (gated_recurrence_kernel<TP, TO><<<grid, 128, 0, stream>>>((const TP*)proj, ld, z_off, x_off, g_off, bz, bx, b_dt, state,

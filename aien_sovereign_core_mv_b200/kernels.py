@@ -160,7 +160,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_collect_wait_errors": [P, P],
         "aien_decay_linear_attention": [P, I, L, I, I, I, P, P, P, P, P, P, L, I, I, I, I, P],
         "aien_gated_rmsnorm": [P, L, P, I, L, P, I, F, P, I, L, I, I, P],
-        "aien_gated_recurrence": [P, I, L, I, I, I, P, P, I, P, P, P, P, P, I, L, I, I, P],
+        "aien_gated_recurrence": [P, I, L, I, I, I, P, P, I, P, P, P, P, P, I, L, I, I, I, P],
+        "aien_decay_linear_attention_chunked": [P, I, L, I, I, I, P, P, P, P, P, P, L, P, I, I, I, I, I, P],
         "aien_latent_prepare": [P, I, L, I, P, P, I, F, P, I, L, I, I, I, I, P, P, P, P, I, I, P],
         "aien_rotate_pairs_rows": [P, I, L, L, P, L, L, I, I, I, I, P, P, P],
         "aien_head_project": [P, I, L, L, P, I, L, L, P, I, L, L, I, I, I, I, P],
@@ -1225,11 +1226,13 @@ def softcap(v: torch.Tensor, cap: float) -> None:
 # ---------------------------------------------------------------------------- mixers with a state of fixed size
 def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
                            slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
-                           num_seqs: int, heads: int, dim: int, vdim: int) -> None:
+                           num_seqs: int, heads: int, dim: int, vdim: int, scratch: Optional[torch.Tensor] = None) -> None:
     """Per head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v = silu of the columns of ``proj`` [T, *]
     at q_off (heads*dim), k_off (heads*dim), v_off (heads*vdim).  ``state`` float32 [slots, heads, dim, vdim]: request s
     of the step (tokens q_start[s]..q_start[s+1]) continues from slot slot_map[s], from zero when its first token has
-    position 0, and leaves its state there.  ``out`` float32 [T, heads*vdim]."""
+    position 0, and leaves its state there.  ``out`` float32 [T, heads*vdim].  With ``scratch`` (float32,
+    ``decay_linear_attention_scratch(T, num_seqs, ...)`` numbers) the chunks of a portion run side by side in three
+    launches (for portions of prompts); without it one CTA walks a portion's chunks in order (single tokens)."""
     _dev(proj, decay, state, slot_map, q_start, positions, out)
     assert proj.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == heads * vdim
     assert decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous()
@@ -1237,9 +1240,23 @@ def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: in
     for t in (slot_map, q_start, positions):
         assert t.dtype == torch.int32
     assert max(q_off, k_off) + heads * dim <= proj.shape[1] and v_off + heads * vdim <= proj.shape[1]
+    if scratch is not None:
+        T = proj.shape[0]
+        assert scratch.dtype == torch.float32 and scratch.is_contiguous() and out.shape[0] == T
+        assert scratch.numel() >= decay_linear_attention_scratch(T, num_seqs, heads, dim, vdim)
+        _check(lib().aien_decay_linear_attention_chunked(_p(proj), dt(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _p(decay),
+                                                         _p(state), _p(slot_map), _p(q_start), _p(positions), _p(out), out.stride(0),
+                                                         _p(scratch), T, int(num_seqs), int(heads), int(dim), int(vdim), _stream()),
+               "decay_linear_attention_chunked")
+        return
     _check(lib().aien_decay_linear_attention(_p(proj), dt(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _p(decay),
                                              _p(state), _p(slot_map), _p(q_start), _p(positions), _p(out), out.stride(0),
                                              int(num_seqs), int(heads), int(dim), int(vdim), _stream()), "decay_linear_attention")
+
+
+def decay_linear_attention_scratch(num_tokens: int, num_seqs: int, heads: int, dim: int, vdim: int) -> int:
+    """float32 numbers the chunked form needs: one state-sized block per chunk of 64 tokens, at most T / 64 + S chunks."""
+    return (num_tokens // 64 + num_seqs) * heads * dim * vdim
 
 
 def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -1254,9 +1271,10 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
 
 def gated_recurrence(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Optional[torch.Tensor], bx: Optional[torch.Tensor],
                      state: torch.Tensor, slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
-                     num_seqs: int, width: int) -> None:
+                     num_seqs: int, width: int, segments: bool = False) -> None:
     """Per channel S_t = (1 - z) S_(t-1) + z c with z = sigmoid(proj[z] + bz), u = proj[x] + bx, c = u + 1/2 (u >= 0) or
-    sigmoid(u) (u < 0); out_t = S_t * silu(proj[g]).  ``state`` float32 [slots, width], slots as in decay_linear_attention."""
+    sigmoid(u) (u < 0); out_t = S_t * silu(proj[g]).  ``state`` float32 [slots, width], slots as in decay_linear_attention.
+    ``segments``: every portion is cut into 32 segments that run side by side (for portions of prompts)."""
     _dev(proj, bz, bx, state, slot_map, q_start, positions, out)
     assert proj.stride(1) == 1 and out.stride(1) == 1 and out.shape[1] == width
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width
@@ -1271,7 +1289,7 @@ def gated_recurrence(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz:
         assert t.dtype == torch.int32
     _check(lib().aien_gated_recurrence(_p(proj), dt(proj), proj.stride(0), int(z_off), int(x_off), int(g_off), _p(bz), _p(bx), bdt,
                                        _p(state), _p(slot_map), _p(q_start), _p(positions), _p(out), dt(out), out.stride(0),
-                                       int(num_seqs), int(width), _stream()), "gated_recurrence")
+                                       int(num_seqs), int(width), 1 if segments else 0, _stream()), "gated_recurrence")
 
 
 # ---------------------------------------------------------------------------- attention over a cached latent

@@ -49,7 +49,8 @@ class DecayLinearAttention(Mixer):
         return CacheNeed("state", state_shape=(self.num_heads, self.head_dim, self.value_dim), state_dtype="float32")
 
     def workspace_bytes(self, lim):
-        return lim.max_tokens * ((2 * self.qk_dim + 2 * self.v_dim) * 4 + self.v_dim * (4 + lim.itemsize) + self.hidden_size * 4) + 8192
+        chunks = K.decay_linear_attention_scratch(lim.max_tokens, lim.max_seqs, self.num_heads, self.head_dim, self.value_dim) * 4
+        return lim.max_tokens * ((2 * self.qk_dim + 2 * self.v_dim) * 4 + self.v_dim * (4 + lim.itemsize) + self.hidden_size * 4) + 8192 + chunks
 
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
         T = ctx.num_tokens
@@ -57,8 +58,12 @@ class DecayLinearAttention(Mixer):
         state = group.storage["state"][run.slot]
         proj = linear(ctx, h, self.w_in, out_dtype=torch.float32)
         o = ctx.workspace.take((T, self.v_dim), torch.float32)
+        scratch = None
+        if not ctx.decode_only:                                         # portions of prompts: their chunks side by side
+            n = K.decay_linear_attention_scratch(T, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim)
+            scratch = ctx.workspace.take((n,), torch.float32)
         K.decay_linear_attention(proj, 0, self.qk_dim, 2 * self.qk_dim, self.decay, state, group.slot_map, ctx.q_start, ctx.positions,
-                                 o, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim)
+                                 o, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim, scratch)
         y = ctx.workspace.take((T, self.v_dim), ctx.dtype)
         K.gated_rmsnorm(o, proj[:, 2 * self.qk_dim + self.v_dim:], self.norm_w, self.norm_eps, y)
         return linear(ctx, y, self.w_o, out_dtype=torch.float32)
@@ -103,5 +108,6 @@ class GatedRecurrence(Mixer):
         state = group.storage["state"][run.slot]
         proj = linear(ctx, h, self.w_in, out_dtype=torch.float32)
         y = ctx.workspace.take((T, W), ctx.dtype)
-        K.gated_recurrence(proj, 0, W, 2 * W, self.b_z, self.b_x, state, group.slot_map, ctx.q_start, ctx.positions, y, ctx.num_seqs, W)
+        K.gated_recurrence(proj, 0, W, 2 * W, self.b_z, self.b_x, state, group.slot_map, ctx.q_start, ctx.positions, y, ctx.num_seqs, W,
+                           segments=not ctx.decode_only)
         return linear(ctx, y, self.w_o, out_dtype=torch.float32)

@@ -165,15 +165,18 @@ def _state_group(shape, slots):
     return st, lambda slot_list: GroupView("state", 16, 0, 0, None, i32(slot_list), {"state": st})
 
 
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("heads,dim,vdim,decay", [(3, 20, 12, [0.5, 0.9, 1.0]), (2, 64, 70, [0.0, 0.999]), (1, 130, 8, [0.97])])
-def test_decayed_linear_attention_in_one_step_and_in_pieces(heads, dim, vdim, decay):
+def test_decayed_linear_attention_in_one_step_and_in_pieces(heads, dim, vdim, decay, chunked):
     """Two requests of unequal length in one step against the token-by-token recurrence; then the same tokens in pieces
-    (33, 1, 1, 2, the rest: across the kernel's chunk of 32) through a slot that another request used before."""
+    (65, 1, 1, 2, the rest: across the kernels' chunks of 32 and 64) through a slot that another request used before.
+    ``chunked``: the form whose chunks run side by side (portions of prompts), else the one that walks them in order."""
     from aien_sovereign_core_mv_b200 import kernels as K
     g = torch.Generator().manual_seed(dim)
     D, eps = 48, 1e-5
-    lens = [77, 5]
+    lens = [150, 5]
     T = sum(lens)
+    scratch = lambda n, S: torch.full((K.decay_linear_attention_scratch(n, S, heads, dim, vdim),), float("nan")).cuda() if chunked else None
     p = {n: (torch.randn(r, D, generator=g) / math.sqrt(D)).double().numpy() for n, r in
          (("q", heads * dim), ("k", heads * dim), ("v", heads * vdim), ("g", heads * vdim))}
     h = torch.randn(T, D, generator=g).double().numpy()
@@ -197,29 +200,30 @@ def test_decayed_linear_attention_in_one_step_and_in_pieces(heads, dim, vdim, de
     want1, S1 = plain(h[lens[0]:])
     out = torch.zeros(T, heads * vdim, dtype=torch.float32).cuda()
     K.decay_linear_attention(proj, 0, heads * dim, 2 * heads * dim, dec, st[1], i32([2, 0]), i32([0, lens[0], T]),
-                             i32(list(range(lens[0])) + list(range(lens[1]))), out, 2, heads, dim, vdim)
+                             i32(list(range(lens[0])) + list(range(lens[1]))), out, 2, heads, dim, vdim, scratch(T, 2))
     H.assert_close(out.cpu().numpy(), np.concatenate([want0, want1]), 2e-5, "two requests in one step")
     H.assert_close(st[1, 2].cpu().numpy(), S0, 2e-5, "state of the first")
     H.assert_close(st[1, 0].cpu().numpy(), S1, 2e-5, "state of the second")
     assert float((st[0] - 7.5).abs().max()) == 0.0 and float((st[1, 1] - 7.5).abs().max()) == 0.0     # other runs and slots untouched
     # the first request again, in pieces, through slot 0 (which holds the second request's state): position 0 starts from zero
     at, got = 0, []
-    for n in [33, 1, 1, 2, lens[0] - 37]:
+    for n in [65, 1, 1, 2, lens[0] - 69]:
         o = torch.zeros(n, heads * vdim, dtype=torch.float32).cuda()
         K.decay_linear_attention(proj[at:at + n], 0, heads * dim, 2 * heads * dim, dec, st[1], i32([0]), i32([0, n]),
-                                 i32(list(range(at, at + n))), o, 1, heads, dim, vdim)
+                                 i32(list(range(at, at + n))), o, 1, heads, dim, vdim, scratch(n, 1))
         got.append(o.cpu().numpy())
         at += n
     H.assert_close(np.concatenate(got), want0, 2e-5, "the same tokens in pieces")
     H.assert_close(st[1, 0].cpu().numpy(), S0, 2e-5, "state after the pieces")
 
 
+@pytest.mark.parametrize("segments", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width", [72, 300])
-def test_gated_recurrence_in_one_step_and_in_pieces(dtype, width):
+def test_gated_recurrence_in_one_step_and_in_pieces(dtype, width, segments):
     from aien_sovereign_core_mv_b200 import kernels as K
     g = torch.Generator().manual_seed(width)
-    lens = [41, 6]
+    lens = [141, 6]
     T = sum(lens)
     proj = (torch.randn(T, 3 * width, generator=g) * 2).cuda()
     bz, bx = torch.randn(width, generator=g).cuda(), torch.randn(width, generator=g).cuda()
@@ -242,13 +246,13 @@ def test_gated_recurrence_in_one_step_and_in_pieces(dtype, width):
     tol = 2e-5 if dtype == torch.float32 else 8e-3
     out = torch.zeros(T, width, dtype=dtype).cuda()
     K.gated_recurrence(proj, 0, width, 2 * width, bz, bx, st[0], i32([1, 0]), i32([0, lens[0], T]),
-                       i32(list(range(lens[0])) + list(range(lens[1]))), out, 2, width)
+                       i32(list(range(lens[0])) + list(range(lens[1]))), out, 2, width, segments)
     H.assert_close(out.float().cpu().numpy(), np.concatenate([want0, want1]), tol, "two requests in one step")
     H.assert_close(st[0, 1].cpu().numpy(), S0, 2e-5, "state of the first")
     at, got = 0, []
-    for n in [3, 1, 2, 5, lens[0] - 11]:
+    for n in [3, 1, 2, 5, 33, lens[0] - 44]:
         o = torch.zeros(n, width, dtype=dtype).cuda()
-        K.gated_recurrence(proj[at:at + n], 0, width, 2 * width, bz, bx, st[0], i32([0]), i32([0, n]), i32(list(range(at, at + n))), o, 1, width)
+        K.gated_recurrence(proj[at:at + n], 0, width, 2 * width, bz, bx, st[0], i32([0]), i32([0, n]), i32(list(range(at, at + n))), o, 1, width, segments)
         got.append(o.float().cpu().numpy())
         at += n
     H.assert_close(np.concatenate(got), want0, tol, "the same tokens in pieces, through a slot used before")
