@@ -62,9 +62,9 @@ latent_prepare_kernel(const TD* __restrict__ d, long ld, int q_rank, const void*
 }
 
 // The rotated part of every query head, moved behind the head's latent query:
-// out[t, h, 0:rot_dim] = rotate(q[t, h, 0:rot_dim]) (first rot_dims numbers in pairs), float32.
-template <typename TQ>
-__global__ void rotate_pairs_rows_kernel(const TQ* __restrict__ q, long ldq, long q_head, float* __restrict__ out, long ldo,
+// out[t, h, 0:rot_dim] = rotate(q[t, h, 0:rot_dim]) (first rot_dims numbers in pairs), the rotation in float32.
+template <typename TQ, typename TO>
+__global__ void rotate_pairs_rows_kernel(const TQ* __restrict__ q, long ldq, long q_head, TO* __restrict__ out, long ldo,
                                          long o_head, int H, int rot_dim, int rot_dims, const float* __restrict__ cos_t,
                                          const float* __restrict__ sin_t) {
     const size_t t = blockIdx.x;
@@ -79,7 +79,7 @@ __global__ void rotate_pairs_rows_kernel(const TQ* __restrict__ q, long ldq, lon
             const float other = to_f(src[i ^ 1]);
             v = (i & 1) ? v * c + other * s : v * c - other * s;
         }
-        out[t * ldo + (size_t)h * o_head + i] = v;
+        out[t * ldo + (size_t)h * o_head + i] = from_f<TO>(v);
     }
 }
 
@@ -320,12 +320,12 @@ AIEN_API int aien_latent_prepare(const void* d, int d_dt, long ld, int q_rank, c
     return launch_status();
 }
 
-AIEN_API int aien_rotate_pairs_rows(const void* q, int q_dt, long ldq, long q_head, float* out, long ldo, long o_head, int T, int H,
+AIEN_API int aien_rotate_pairs_rows(const void* q, int q_dt, long ldq, long q_head, void* out, int o_dt, long ldo, long o_head, int T, int H,
                                     int rot_dim, int rot_dims, const float* cos_t, const float* sin_t, cudaStream_t stream) {
     if (T <= 0 || H <= 0 || rot_dim <= 0) return 0;
     if (rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || (rot_dims > 0 && (cos_t == nullptr || sin_t == nullptr))) return AIEN_E_SHAPE;
-    AIEN_DISPATCH_DTYPE(q_dt, TQ, (rotate_pairs_rows_kernel<TQ><<<T, 128, 0, stream>>>((const TQ*)q, ldq, q_head, out, ldo, o_head, H,
-                                                                                    rot_dim, rot_dims, cos_t, sin_t)));
+    AIEN_DISPATCH_DTYPE(q_dt, TQ, AIEN_DISPATCH_DTYPE(o_dt, TO,
+        (rotate_pairs_rows_kernel<TQ, TO><<<T, 128, 0, stream>>>((const TQ*)q, ldq, q_head, (TO*)out, ldo, o_head, H, rot_dim, rot_dims, cos_t, sin_t))));
     return launch_status();
 }
 

@@ -163,7 +163,9 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_gated_recurrence": [P, I, L, I, I, I, P, P, I, P, P, P, P, P, I, L, I, I, I, P],
         "aien_decay_linear_attention_chunked": [P, I, L, I, I, I, P, P, P, P, P, P, L, P, I, I, I, I, I, P],
         "aien_latent_prepare": [P, I, L, I, P, P, I, F, P, I, L, I, I, I, I, P, P, P, P, I, I, P],
-        "aien_rotate_pairs_rows": [P, I, L, L, P, L, L, I, I, I, I, P, P, P],
+        "aien_rotate_pairs_rows": [P, I, L, L, P, I, L, L, I, I, I, I, P, P, P],
+        "aien_latent_attention_tc": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
+        "aien_latent_attention_tc_supports": [I, I],
         "aien_head_project": [P, I, L, L, P, I, L, L, P, I, L, L, I, I, I, I, P],
         "aien_latent_attention": [P, L, P, I, P, I, P, P, P, P, I, L, I, I, I, I, I, I, F, P, P],
         "aien_post_norm_add": [P, P, I, I, c_size_t, P, I, F, F, P, I, F, P, I, I, I, P],
@@ -1324,14 +1326,14 @@ def latent_prepare(d: torch.Tensor, q_rank: int, wq: Optional[torch.Tensor], eps
 def rotate_pairs_rows(q: torch.Tensor, q_head: int, col0: int, out: torch.Tensor, o_head: int, ocol0: int, heads: int, rot_dim: int,
                       rot_dims: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor]) -> None:
     """out[t, h*o_head + ocol0 + i] = q[t, h*q_head + col0 + i], i < rot_dim, the first ``rot_dims`` of them rotated in
-    neighbouring pairs by the token's angle; out float32."""
+    neighbouring pairs by the token's angle (the rotation itself in float32)."""
     _dev(q, out, cos, sin)
     T = q.shape[0]
-    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == torch.float32
+    assert q.stride(1) == 1 and out.stride(1) == 1
     if rot_dims:
         assert cos is not None and tuple(cos.shape) == (T, rot_dims // 2) and cos.is_contiguous() and sin.is_contiguous()
     qv, ov = q[:, col0:], out[:, ocol0:]
-    _check(lib().aien_rotate_pairs_rows(_p(qv), dt(q), q.stride(0), int(q_head), _p(ov), out.stride(0), int(o_head), T, int(heads),
+    _check(lib().aien_rotate_pairs_rows(_p(qv), dt(q), q.stride(0), int(q_head), _p(ov), dt(out), out.stride(0), int(o_head), T, int(heads),
                                         int(rot_dim), int(rot_dims), _p(cos), _p(sin), _stream()), "rotate_pairs_rows")
 
 
@@ -1364,3 +1366,29 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
                                        _p(positions), None, _p(out), dt(out), out.stride(0), T, int(heads), int(kv_rank),
                                        int(rot_dim), int(page_size), int(window), float(scale), _p(sinks), _stream()),
            "latent_attention")
+
+
+_LATENT_IMPL = __import__("os").environ.get("AIEN_B200_LATENT_ATTENTION", "tc").strip().lower()     # "tc" | "plain"
+
+
+def latent_attention_tc_supports(dtype: torch.dtype, kv_rank: int, rot_dim: int) -> bool:
+    """Whether the tensor-core kernel takes this case: bfloat16, a latent of 64 / 128 / 256 / 512, a rotated part that is a multiple of 16."""
+    return _LATENT_IMPL != "plain" and dtype == torch.bfloat16 and bool(lib().aien_latent_attention_tc_supports(int(kv_rank), int(rot_dim)))
+
+
+def latent_attention_tc(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, max_blocks: int, q_start: torch.Tensor,
+                        positions: torch.Tensor, out: torch.Tensor, num_seqs: int, heads: int, kv_rank: int, rot_dim: int,
+                        page_size: int, window: int, scale: float, sinks: Optional[torch.Tensor]) -> None:
+    """latent_attention on the tensor cores.  q bfloat16 [T, heads*(kv_rank + rot_dim)] and out bfloat16 [T, heads*kv_rank],
+    both contiguous; the T tokens are the portions q_start[s]..q_start[s+1] of ``num_seqs`` requests (row s of the block
+    table), each portion's positions counting up from positions[q_start[s]]."""
+    _dev(q, cache, block_table, q_start, positions, out, sinks)
+    T, D = q.shape[0], kv_rank + rot_dim
+    assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and cache.shape[-1] == D
+    assert q.shape[1] == heads * D and tuple(out.shape) == (T, heads * kv_rank)
+    assert block_table.dtype == torch.int32 and q_start.dtype == torch.int32 and positions.dtype == torch.int32
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == heads)
+    _check(lib().aien_latent_attention_tc(_p(q), _p(cache), _p(block_table), int(max_blocks), _p(q_start), _p(positions), _p(out), T,
+                                          int(num_seqs), int(heads), int(kv_rank), int(rot_dim), int(page_size), int(window),
+                                          float(scale), _p(sinks), _stream()), "latent_attention_tc")

@@ -104,13 +104,18 @@ class LatentAttention(Mixer):
         K.latent_prepare(d, self.q_rank, self.dq_norm, self.norm_eps, cq, self.q_rank, self.kv_rank, self.rot_dim, rdims,
                          self.dkv_norm, cos, sin, group.slot_map if writes else None, cache if writes else None)
         q = linear(ctx, cq, self.w_uq, out_dtype=torch.float32)         # per head: unrotated | rotated part, before rotation
-        qf = ws.take((T, n * self.row), torch.float32)                  # per head: the query in the latent | rotated part
+        tc = K.latent_attention_tc_supports(cache.dtype, self.kv_rank, self.rot_dim) and ctx.dtype == torch.bfloat16
+        qf = ws.take((T, n * self.row), torch.bfloat16 if tc else torch.float32)    # per head: the query in the latent | rotated part
         K.head_project(q, self.q_head, 0, self.w_uk_t, qf, self.row, 0)
         if self.rot_dim:
             K.rotate_pairs_rows(q, self.q_head, self.head_dim, qf, self.row, self.kv_rank, n, self.rot_dim, rdims, cos, sin)
         mixed = ws.take((T, n * self.kv_rank), ctx.dtype)
-        K.latent_attention(qf, cache, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, mixed, n, self.kv_rank,
-                           self.rot_dim, group.page_size, self.window, self.scale, self.sinks)
+        if tc:
+            K.latent_attention_tc(qf, cache, group.block_table, group.max_blocks, ctx.q_start, ctx.positions, mixed, ctx.num_seqs, n,
+                                  self.kv_rank, self.rot_dim, group.page_size, self.window, self.scale, self.sinks)
+        else:
+            K.latent_attention(qf, cache, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, mixed, n, self.kv_rank,
+                               self.rot_dim, group.page_size, self.window, self.scale, self.sinks)
         o = ws.take((T, n * self.value_dim), ctx.dtype)
         K.head_project(mixed, self.kv_rank, 0, self.w_uv, o, self.value_dim, 0)
         return linear(ctx, o, self.w_o, out_dtype=torch.float32)

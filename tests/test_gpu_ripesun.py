@@ -314,17 +314,22 @@ def test_one_product_per_head(dtype, heads, n, k):
     assert float(np.abs(got[:, :, n:]).max()) == 0.0 and float(out[:, 0].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("window,page,heads,r,rd", [(21, 16, 5, 40, 8), (64, 16, 17, 128, 32), (0, 8, 1, 96, 16), (16, 16, 4, 64, 64), (7, 32, 3, 520, 0)])
-def test_latent_attention_sees_its_window_and_the_sink(dtype, window, page, heads, r, rd):
-    """Queries at several positions of a request of 150 tokens whose pages lie scattered.  The keys just inside the
-    window (distance window - 1), just outside (distance window), at position 0 and on both sides of a page border are
-    scaled so that each would take nearly all the weight if it were seen; one head's sink is made large."""
+@pytest.mark.parametrize("dtype,impl", [(torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "tc")])
+@pytest.mark.parametrize("window,page,heads,r,rd", [(21, 16, 5, 40, 8), (64, 16, 17, 128, 32), (0, 8, 1, 96, 16), (16, 16, 4, 64, 64),
+                                                     (7, 32, 3, 520, 0), (100, 16, 6, 256, 16), (0, 16, 16, 512, 64)])
+def test_latent_attention_sees_its_window_and_the_sink(dtype, impl, window, page, heads, r, rd):
+    """Portions at several places of a request of 150 tokens whose pages lie scattered (each portion as a request of its
+    own over the same pages): the first tokens, both sides of a page border, the end.  The keys just inside the window
+    (distance window - 1), just outside (distance window) and at position 0 are scaled so that each would take nearly all
+    the weight if it were seen; one head's sink is made large.  ``impl``: the plain kernel, or the tensor-core one."""
     from aien_sovereign_core_mv_b200 import kernels as K
+    if impl == "tc" and not K.latent_attention_tc_supports(dtype, r, rd):
+        pytest.skip("the tensor-core kernel does not take this size")
     g = torch.Generator().manual_seed(window + r)
     n, D, scale = 150, r + rd, 0.2
     rows = torch.randn(n, D, generator=g) * 0.5
-    qpos = [0, 1, page - 1, page, 2 * page, 99, 100, 149]
+    portions = [(0, 3), (page - 2, 4), (2 * page, 1), (60, 70), (149, 1)]
+    qpos = [p0 + i for p0, m in portions for i in range(m)]
     loud = {p - far for p in qpos for far in ([window - 1, window] if window else [p]) if p - far >= 0}
     for j in sorted(loud):
         rows[j] *= 3.0
@@ -333,23 +338,32 @@ def test_latent_attention_sees_its_window_and_the_sink(dtype, window, page, head
     cache = torch.zeros((max(order) + 1) * page, D, dtype=dtype)
     for j in range(n):
         cache[order[j // page] * page + j % page] = rows[j]
-    bt = torch.full((2, 64), -1, dtype=torch.int32)
-    bt[1, :(n + page - 1) // page] = torch.tensor(order[:(n + page - 1) // page], dtype=torch.int32)
-    q = torch.randn(len(qpos), heads * D, generator=g) * 0.7
+    bt = torch.full((len(portions), 64), -1, dtype=torch.int32)
+    bt[:, :(n + page - 1) // page] = torch.tensor(order[:(n + page - 1) // page], dtype=torch.int32)
+    qdt = torch.bfloat16 if impl == "tc" else torch.float32
+    q = (torch.randn(len(qpos), heads * D, generator=g) * 0.7).to(qdt)
     sinks = torch.randn(heads, generator=g)
     sinks[0] = 6.0
     out = torch.zeros(len(qpos), heads * r, dtype=dtype).cuda()
-    K.latent_attention(q.cuda(), cache.cuda(), bt.cuda(), 64, i32([1] * len(qpos)), i32(qpos), out, heads, r, rd, page, window, scale, sinks.cuda())
+    seq_of = [s for s, (_, m) in enumerate(portions) for _ in range(m)]
+    starts = [0]
+    for _, m in portions:
+        starts.append(starts[-1] + m)
+    if impl == "tc":
+        K.latent_attention_tc(q.cuda(), cache.cuda(), bt.cuda(), 64, i32(starts), i32(qpos), out, len(portions), heads, r, rd, page, window,
+                              scale, sinks.cuda())
+    else:
+        K.latent_attention(q.cuda(), cache.cuda(), bt.cuda(), 64, i32(seq_of), i32(qpos), out, heads, r, rd, page, window, scale, sinks.cuda())
     rn, qn = rows.double().numpy(), q.double().numpy().reshape(len(qpos), heads, D)
     want = np.zeros((len(qpos), heads, r))
     for t, p in enumerate(qpos):
         seen = [j for j in range(n) if j <= p and (window == 0 or p - j < window)]
         for hd in range(heads):
-            s = np.array([qn[t, hd] @ rn[j] * scale for j in seen])
-            m = max(s.max(), float(sinks[hd]))
-            e = np.exp(s - m)
+            sc = np.array([qn[t, hd] @ rn[j] * scale for j in seen])
+            m = max(sc.max(), float(sinks[hd]))
+            e = np.exp(sc - m)
             want[t, hd] = (e[:, None] * rn[seen][:, :r]).sum(0) / (e.sum() + math.exp(float(sinks[hd]) - m))
-    H.assert_close(out.float().cpu().numpy().reshape(len(qpos), heads, r), want, 1e-5 if dtype == torch.float32 else 1e-2, "weighted latents")
+    H.assert_close(out.float().cpu().numpy().reshape(len(qpos), heads, r), want, 1e-5 if dtype == torch.float32 else 1.5e-2, "weighted latents")
 
 
 # ------------------------------------------------------------------ whole models
