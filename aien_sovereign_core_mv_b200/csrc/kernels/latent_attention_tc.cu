@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(LX_THREADS, 1)
 latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                            const int* __restrict__ positions, int S, __nv_bfloat16* __restrict__ out,
-                           int H, int rd, int page_size, int window, float scale_log2e, const float* __restrict__ sinks) {
+                           int H, int rd, int page_size, int window, float scale_log2e, const float* __restrict__ sinks,
+                           int ksplit, float* __restrict__ part_o, float* __restrict__ part_ml) {
     constexpr int DT = R / 16;                   // n8 tiles of this warp's half of the channels
     const int D = R + rd, STR = D + 8, CH = D / 8, KS = D / 16;
     extern __shared__ __align__(16) uint8_t lx_smem[];
@@ -100,7 +101,11 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     const bool active = slab * 16 < nrows;
 
     const int kb_begin = first / LX_BN, kb_end = pos_hi / LX_BN;
-    for (int kb = kb_begin; kb <= kb_end; ++kb) {
+    if (ksplit > 1) {                                                      // Q must have landed even if this CTA gets no block
+        lx_cp_async_wait_all();
+        __syncthreads();
+    }
+    for (int kb = kb_begin + (int)blockIdx.y; kb <= kb_end; kb += ksplit) {
         for (int idx = tid; idx < LX_BN * CH; idx += LX_THREADS) {
             const int r = idx / CH, ch = idx - r * CH;
             const int key = kb * LX_BN + r;
@@ -200,6 +205,33 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         __syncthreads();                                                   // every warp is done with this block
     }
 
+    if (ksplit > 1) {
+        // this CTA saw only some of the key blocks: its running maximum, its sum and its unnormalised weighted sum go to
+        // the scratch, and a second launch combines the CTAs of a row
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1); l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+        if (c == 0) {
+            stat[half * LX_BM + ra] = l_run[0];
+            stat[half * LX_BM + rb] = l_run[1];
+        }
+        __syncthreads();
+        l_run[0] += stat[(half ^ 1) * LX_BM + ra];
+        l_run[1] += stat[(half ^ 1) * LX_BM + rb];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = r == 0 ? ra : rb;
+            if (row >= nrows) continue;
+            const size_t slot = ((size_t)qs * H + row0 + row) * ksplit + blockIdx.y;
+            if (half == 0 && c == 0) {
+                part_ml[slot * 2] = m_run[r];
+                part_ml[slot * 2 + 1] = l_run[r];
+            }
+            float* dst = part_o + slot * R + half * (R / 2);
+#pragma unroll
+            for (int d = 0; d < DT; ++d) *reinterpret_cast<float2*>(dst + d * 8 + 2 * c) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
+        }
+        return;
+    }
     // the denominators: this thread's partial sums, its quad's, the other half's
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1); l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
@@ -229,20 +261,113 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     }
 }
 
+// out[row] = sum_s 2^(m_s - M) o_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)), M = max over the row's parts and the sink
+template <int R>
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int ksplit,
+                                              const float* __restrict__ sinks, int H, __nv_bfloat16* __restrict__ out) {
+    const size_t row = blockIdx.x;
+    const float sk = sinks != nullptr ? sinks[row % H] * 1.4426950408889634f : -INFINITY;
+    float M = sk;
+    for (int s = 0; s < ksplit; ++s) M = fmaxf(M, part_ml[(row * ksplit + s) * 2]);
+    float den = (sinks != nullptr && M != -INFINITY) ? exp2f(sk - M) : 0.f;
+    for (int s = 0; s < ksplit; ++s) {
+        const float m = part_ml[(row * ksplit + s) * 2];
+        if (m != -INFINITY) den += exp2f(m - M) * part_ml[(row * ksplit + s) * 2 + 1];
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    for (int ch = threadIdx.x; ch < R; ch += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < ksplit; ++s) {
+            const float m = part_ml[(row * ksplit + s) * 2];
+            if (m != -INFINITY) acc += exp2f(m - M) * part_o[(row * ksplit + s) * R + ch];
+        }
+        out[row * R + ch] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 template <int R>
 static int launch_latent_tc(const void* q, const void* cache, const int* bt, int max_blocks, const int* q_start, const int* positions,
                             int T, int S, void* out, int H, int rd, int page_size, int window, float scale, const float* sinks,
-                            cudaStream_t stream) {
+                            int ksplit, float* part_o, float* part_ml, cudaStream_t stream) {
     const int D = R + rd;
     const size_t smem = (size_t)(LX_BM + LX_BN) * (D + 8) * 2 + (size_t)LX_BM * LX_PSTR * 2 + 2 * LX_BM * sizeof(float);
     if (smem > 227 * 1024) return AIEN_E_SHAPE;
     auto kern = latent_attention_tc_kernel<R>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
     const long tiles = ((long)T * H) / LX_BM + S;
-    kern<<<dim3((unsigned)tiles), LX_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, max_blocks, q_start,
-                                                             positions, S, (__nv_bfloat16*)out, H, rd, page_size, window,
-                                                             scale * 1.4426950408889634f, sinks);
+    kern<<<dim3((unsigned)tiles, ksplit), LX_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, max_blocks, q_start,
+                                                                     positions, S, (__nv_bfloat16*)out, H, rd, page_size, window,
+                                                                     scale * 1.4426950408889634f, sinks, ksplit, part_o, part_ml);
+    if (ksplit > 1)
+        latent_attention_merge_kernel<R><<<dim3((unsigned)((long)T * H)), 128, 0, stream>>>(part_o, part_ml, ksplit, sinks, H, (__nv_bfloat16*)out);
     return launch_status();
+}
+
+
+// ---------------------------------------------------------------- one product per head, on the tensor cores
+// C[m, h, n] = sum_k A[m, h, k] * W[h, n, k] (see head_project_kernel) for bfloat16 A and W: tiles of 64 x 64 per CTA of
+// four warps, k in steps of 64 through shared memory (cp.async), mma.sync.m16n8k16 with float32 accumulation.
+constexpr int HT_BM = 64, HT_BN = 64, HT_BK = 64, HT_STR = HT_BK + 8;
+
+template <typename TC>
+__global__ void __launch_bounds__(128)
+head_project_tc_kernel(const __nv_bfloat16* __restrict__ A, long lda, long a_head, const __nv_bfloat16* __restrict__ W, long w_head,
+                       TC* __restrict__ C, long ldc, long c_head, int M, int N, int K) {
+    __shared__ __align__(16) __nv_bfloat16 As[HT_BM * HT_STR];
+    __shared__ __align__(16) __nv_bfloat16 Ws[HT_BN * HT_STR];
+    const uint32_t As_u = (uint32_t)__cvta_generic_to_shared(As), Ws_u = (uint32_t)__cvta_generic_to_shared(Ws);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int mh = warp & 1, nh = warp >> 1, g = lane >> 2, c = lane & 3;
+    const int m0 = blockIdx.y * HT_BM, n0 = blockIdx.x * HT_BN, h = blockIdx.z;
+    A += (size_t)h * a_head;
+    W += (size_t)h * w_head;
+    C += (size_t)h * c_head;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HT_BK) {
+        for (int idx = tid; idx < HT_BM * (HT_BK / 8); idx += 128) {
+            const int r = idx >> 3, ch = idx & 7;
+            const bool kin = k0 + ch * 8 < K;
+            const bool va = kin && m0 + r < M, vw = kin && n0 + r < N;
+            lx_cp_async16(As_u + (uint32_t)(r * HT_STR + ch * 8) * 2, A + (size_t)(va ? m0 + r : 0) * lda + (va ? k0 + ch * 8 : 0), va);
+            lx_cp_async16(Ws_u + (uint32_t)(r * HT_STR + ch * 8) * 2, W + (size_t)(vw ? n0 + r : 0) * K + (vw ? k0 + ch * 8 : 0), vw);
+        }
+        lx_cp_async_commit();
+        lx_cp_async_wait_all();
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HT_BK / 16; ++kk) {
+            uint32_t a[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+                lx_ldmatrix_x4(As_u + (uint32_t)((mh * 32 + mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * HT_STR + kk * 16 + (lane >> 4) * 8) * 2,
+                               a[mt][0], a[mt][1], a[mt][2], a[mt][3]);
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const int mi = lane >> 3;
+                uint32_t b0, b1, b2, b3;
+                lx_ldmatrix_x4(Ws_u + (uint32_t)((nh * 32 + (j + (mi >> 1)) * 8 + (lane & 7)) * HT_STR + kk * 16 + (mi & 1) * 8) * 2, b0, b1, b2, b3);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    lx_mma(acc[mt][j], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+                    lx_mma(acc[mt][j + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int m = m0 + mh * 32 + mt * 16 + g + (e >> 1) * 8, n = n0 + nh * 32 + j * 8 + 2 * c + (e & 1);
+                if (m < M && n < N) C[(size_t)m * ldc + n] = from_f<TC>(acc[mt][j][e]);
+            }
 }
 
 }  // namespace aien
@@ -257,17 +382,35 @@ AIEN_API int aien_latent_attention_tc_supports(int kv_rank, int rot_dim) {
 
 // q bfloat16 [T, H, kv_rank + rot_dim] (contiguous), cache bfloat16 [slots, kv_rank + rot_dim], out bfloat16 [T, H, kv_rank].
 // The step's T tokens are the portions q_start[s] .. q_start[s + 1] of S requests; positions[t] is token t's position.
+// ksplit > 1: the key blocks of every tile are dealt out to ksplit CTAs (for steps with few tiles); part_o (float32,
+// T * H * ksplit * kv_rank) and part_ml (float32, T * H * ksplit * 2) hold their partial results for the merging launch.
 AIEN_API int aien_latent_attention_tc(const void* q, const void* cache, const int* block_table, int max_blocks, const int* q_start,
                                       const int* positions, void* out, int T, int S, int H, int kv_rank, int rot_dim, int page_size,
-                                      int window, float scale, const float* sinks, cudaStream_t stream) {
+                                      int window, float scale, const float* sinks, int ksplit, float* part_o, float* part_ml,
+                                      cudaStream_t stream) {
     if (T <= 0 || S <= 0) return 0;
     if (H <= 0 || page_size <= 0 || window < 0 || !aien_latent_attention_tc_supports(kv_rank, rot_dim)) return AIEN_E_SHAPE;
     if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 3)) return AIEN_E_ALIGN;
+    if (ksplit < 1 || ksplit > 65535 || (ksplit > 1 && (part_o == nullptr || part_ml == nullptr || ((uintptr_t)part_o & 7)))) return AIEN_E_SHAPE;
 #define LX_CASE(RV)                                                                                                              \
     if (kv_rank == RV)                                                                                                           \
         return launch_latent_tc<RV>(q, cache, block_table, max_blocks, q_start, positions, T, S, out, H, rot_dim, page_size, window, \
-                                    scale, sinks, stream);
+                                    scale, sinks, ksplit, part_o, part_ml, stream);
     LX_CASE(64) LX_CASE(128) LX_CASE(256) LX_CASE(512)
 #undef LX_CASE
     return AIEN_E_SHAPE;
+}
+
+// A bfloat16 [M, lda] (head h at column h * a_head), W bfloat16 [heads, N, K], C [M, ldc] (head h at column h * c_head).
+// K, lda and a_head multiples of 8, A and W 16-byte aligned.
+AIEN_API int aien_head_project_tc(const void* A, long lda, long a_head, const void* W, void* C, int c_dt, long ldc, long c_head,
+                                  int M, int N, int K, int heads, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || heads <= 0) return 0;
+    if (K <= 0 || heads > 65535) return AIEN_E_SHAPE;
+    if ((K & 7) || (lda & 7) || (a_head & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
+    dim3 grid((N + HT_BN - 1) / HT_BN, (M + HT_BM - 1) / HT_BM, heads);
+    if (grid.y > 65535) return AIEN_E_SHAPE;
+    AIEN_DISPATCH_DTYPE(c_dt, TC, (head_project_tc_kernel<TC><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)A, lda, a_head, (const __nv_bfloat16*)W,
+                                                                                     (long)N * K, (TC*)C, ldc, c_head, M, N, K)));
+    return launch_status();
 }

@@ -48,6 +48,81 @@ post_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_part
     for (int i = threadIdx.x; i < H; i += blockDim.x) h[base + i] = from_f<TH>(row[i] * scale2 * load_dyn(w_next, wndt, i));
 }
 
+
+// The same for rows of whole float4 vectors (H % 4 == 0, 16-byte aligned rows): every thread owns up to NV vectors of
+// the row and keeps them in registers between the passes, with all loads of a pass in flight at once; the CTA has as
+// many threads as the row has vectors (up to 512).  Parts are added in the order of the plain kernel; which of the two
+// kernels a row takes follows from H and the pointers alone, never from the step.
+__device__ __forceinline__ float4 pn_w4(const void* w, int wdt, int v) {
+    if (wdt == AIEN_DT_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + 4 * v);
+    return ld_act4(reinterpret_cast<const __nv_bfloat16*>(w) + 4 * v);
+}
+__device__ __forceinline__ void pn_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void pn_store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<uint32_t*>(&a);
+    r.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename TA, typename TH, int NV>
+__global__ void __launch_bounds__(512)
+post_norm_add_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_parts, size_t a_stride,
+                         const void* __restrict__ w, int wdt, float eps, float mult,
+                         const void* __restrict__ w_next, int wndt, float eps_next, TH* __restrict__ h, int H) {
+    __shared__ float red[32];
+    const int nvec = H >> 2;
+    const size_t base = (size_t)blockIdx.x * H;
+    float4 y[NV], xv[NV], wv[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        y[j] = xv[j] = wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (v < nvec) {
+            wv[j] = pn_w4(w, wdt, v);
+            xv[j] = *reinterpret_cast<const float4*>(x + base + 4 * (size_t)v);
+            for (int p = 0; p < a_parts; ++p) {
+                const float4 t = ld_act4(a + (size_t)p * a_stride + base + 4 * (size_t)v);
+                y[j].x += t.x; y[j].y += t.y; y[j].z += t.z; y[j].w += t.w;
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) ss += y[j].x * y[j].x + y[j].y * y[j].y + y[j].z * y[j].z + y[j].w * y[j].w;
+    const float scale = mult / sqrtf(block_sum(ss, red) / (float)H + eps);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        xv[j] = make_float4(xv[j].x + y[j].x * scale * wv[j].x, xv[j].y + y[j].y * scale * wv[j].y,
+                            xv[j].z + y[j].z * scale * wv[j].z, xv[j].w + y[j].w * scale * wv[j].w);
+        if (v < nvec) {
+            *reinterpret_cast<float4*>(x + base + 4 * (size_t)v) = xv[j];
+            ss2 += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+        }
+    }
+    if (h == nullptr) return;
+    if (w_next == nullptr) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int v = threadIdx.x + j * blockDim.x;
+            if (v < nvec) pn_store4(h + base + 4 * (size_t)v, xv[j]);
+        }
+        return;
+    }
+    const float scale2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)H + eps_next);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) {
+            const float4 n = pn_w4(w_next, wndt, v);
+            pn_store4(h + base + 4 * (size_t)v, make_float4(xv[j].x * scale2 * n.x, xv[j].y * scale2 * n.y, xv[j].z * scale2 * n.z, xv[j].w * scale2 * n.w));
+        }
+    }
+}
+
 template <typename TW>
 __global__ void embed_gather_scaled_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                                            int H, int V, float scale) {
@@ -86,6 +161,22 @@ using namespace aien;
 template <typename TA, typename TH>
 static int launch_post_norm_add(size_t smem, cudaStream_t stream, float* x, const TA* a, int a_parts, size_t a_stride, const void* w,
                                 int w_dt, float eps, float mult, const void* w_next, int wn_dt, float eps_next, TH* h, int T, int H) {
+    {
+        const int nvec = H >> 2;
+        const int threads = nvec >= 512 ? 512 : ((nvec + 31) & ~31);
+        const int wsz = w_dt == AIEN_DT_F32 ? 15 : 7, wnsz = wn_dt == AIEN_DT_F32 ? 15 : 7, asz = sizeof(TA) == 4 ? 15 : 7, hsz = sizeof(TH) == 4 ? 15 : 7;
+        const bool aligned = (H & 3) == 0 && threads > 0 && nvec <= threads * 4 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)a & asz) == 0 &&
+                             ((uintptr_t)w & wsz) == 0 && ((uintptr_t)w_next & wnsz) == 0 && ((uintptr_t)h & hsz) == 0 && (a_stride & 3) == 0;
+        if (aligned) {
+            if (nvec <= threads)
+                post_norm_add_vec_kernel<TA, TH, 1><<<T, threads, 0, stream>>>(x, a, a_parts, a_stride, w, w_dt, eps, mult, w_next, wn_dt, eps_next, h, H);
+            else if (nvec <= 2 * threads)
+                post_norm_add_vec_kernel<TA, TH, 2><<<T, threads, 0, stream>>>(x, a, a_parts, a_stride, w, w_dt, eps, mult, w_next, wn_dt, eps_next, h, H);
+            else
+                post_norm_add_vec_kernel<TA, TH, 4><<<T, threads, 0, stream>>>(x, a, a_parts, a_stride, w, w_dt, eps, mult, w_next, wn_dt, eps_next, h, H);
+            return 0;
+        }
+    }
     auto kern = post_norm_add_kernel<TA, TH>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return AIEN_E_STATE;

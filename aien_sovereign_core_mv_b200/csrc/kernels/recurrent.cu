@@ -210,12 +210,20 @@ la_state_scan_kernel(float* __restrict__ U, const float* __restrict__ decay, flo
     const float l2 = log2f(decay[h]);
     const float full = decay_pow(l2, LC);
     const int nch = (len + LC - 1) / LC;
-    for (int k = 0; k < nch; ++k) {
-        float* u = U + ((size_t)(base + k) * H + h) * E + e;
-        const float uv = *u;
-        *u = Sv;
-        const int n = min(LC, len - k * LC);
-        Sv = fmaf(n == LC ? full : decay_pow(l2, n), Sv, uv);
+    const size_t cstride = (size_t)H * E;
+    float* u0 = U + ((size_t)base * H + h) * E + e;
+    for (int k0 = 0; k0 < nch; k0 += 8) {                                  // the loads of eight chunks in flight, then their updates in order
+        float uv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) uv[i] = (k0 + i < nch) ? __ldcg(u0 + (size_t)(k0 + i) * cstride) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (k0 + i < nch) {
+                u0[(size_t)(k0 + i) * cstride] = Sv;
+                const int n = min(LC, len - (k0 + i) * LC);
+                Sv = fmaf(n == LC ? full : decay_pow(l2, n), Sv, uv[i]);
+            }
+        }
     }
     *st = Sv;
 }
@@ -258,6 +266,7 @@ la_chunk_output_kernel(const TP* __restrict__ proj, long ld, int q_off, int k_of
         for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
     // scores of the chunk: rows i = ty*4.., keys j = tx*4..; tiles wholly above the diagonal stay zero
     if (tx <= ty) {
+#pragma unroll 4
         for (int d = 0; d < dim; ++d) {
             const float4 qq = *reinterpret_cast<const float4*>(&Qt[d * LPAD + ty * 4]);
             const float4 kk = *reinterpret_cast<const float4*>(&Kt[d * LPAD + tx * 4]);
@@ -292,19 +301,30 @@ la_chunk_output_kernel(const TP* __restrict__ proj, long ld, int q_off, int k_of
 #pragma unroll
             for (int b = 0; b < 4; ++b) o1[a][b] = fmaf(a4[a], v4[b], o1[a][b]);
     }
-    const float* p = P + ((size_t)c * H + h) * dim * vd + v0 + tx * 4;
-    const bool vec = (vd & 3) == 0 && v0 + tx * 4 + 3 < vd;
+    // the state before the chunk, [dim][LVT] of it, into the space of the keys (used up since the scores)
+    {
+        const float* p = P + ((size_t)c * H + h) * dim * vd + v0;
+        const bool vec = (vd & 3) == 0;
+        for (int idx = tid; idx < dim * (LVT / 4); idx += 256) {
+            const int d = idx / (LVT / 4), v4i = (idx % (LVT / 4)) * 4;
+            float4 pp = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (vec && v0 + v4i + 3 < vd) {
+                pp = __ldcg(reinterpret_cast<const float4*>(p + (size_t)d * vd + v4i));
+            } else {
+                if (v0 + v4i < vd) pp.x = p[(size_t)d * vd + v4i];
+                if (v0 + v4i + 1 < vd) pp.y = p[(size_t)d * vd + v4i + 1];
+                if (v0 + v4i + 2 < vd) pp.z = p[(size_t)d * vd + v4i + 2];
+                if (v0 + v4i + 3 < vd) pp.w = p[(size_t)d * vd + v4i + 3];
+            }
+            *reinterpret_cast<float4*>(&Kt[d * LPAD + v4i]) = pp;
+        }
+    }
+    __syncthreads();
+#pragma unroll 4
     for (int d = 0; d < dim; ++d) {
         const float4 qq = *reinterpret_cast<const float4*>(&Qt[d * LPAD + ty * 4]);
-        float p4[4];
-        if (vec) {
-            const float4 pp = *reinterpret_cast<const float4*>(p + (size_t)d * vd);
-            p4[0] = pp.x; p4[1] = pp.y; p4[2] = pp.z; p4[3] = pp.w;
-        } else {
-#pragma unroll
-            for (int b = 0; b < 4; ++b) p4[b] = (v0 + tx * 4 + b < vd) ? p[(size_t)d * vd + b] : 0.f;
-        }
-        const float q4[4] = {qq.x, qq.y, qq.z, qq.w};
+        const float4 pp = *reinterpret_cast<const float4*>(&Kt[d * LPAD + tx * 4]);
+        const float q4[4] = {qq.x, qq.y, qq.z, qq.w}, p4[4] = {pp.x, pp.y, pp.z, pp.w};
 #pragma unroll
         for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -413,12 +433,23 @@ gated_recurrence_segments_kernel(const TP* __restrict__ proj, long ld, int z_off
     const float bzc = (live && bz) ? load_dyn(bz, bdt, c) : 0.f, bxc = (live && bx) ? load_dyn(bx, bdt, c) : 0.f;
     float a = 1.f, b = 0.f;
     if (live) {
-        for (int t = lo; t < hi; ++t) {
-            const TP* row = proj + (size_t)t * ld + c;
-            const float z = sigmoid_f(to_f(row[z_off]) + bzc), u = to_f(row[x_off]) + bxc;
-            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-            b = (1.0f - z) * b + z * cand;
-            a *= (1.0f - z);
+        for (int t = lo; t < hi; t += 8) {
+            float pz[8], px[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const TP* row = proj + (size_t)min(t + i, hi - 1) * ld + c;
+                pz[i] = to_f(row[z_off]);
+                px[i] = to_f(row[x_off]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (t + i < hi) {
+                    const float z = sigmoid_f(pz[i] + bzc), u = px[i] + bxc;
+                    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+                    b = (1.0f - z) * b + z * cand;
+                    a *= (1.0f - z);
+                }
+            }
         }
     }
     As[seg][lane] = a;
@@ -428,12 +459,24 @@ gated_recurrence_segments_kernel(const TP* __restrict__ proj, long ld, int z_off
     float* st = state + (size_t)slot_map[s] * W + c;
     float Sv = positions[t0] == 0 ? 0.f : *st;
     for (int k = 0; k < seg; ++k) Sv = As[k][lane] * Sv + Bs[k][lane];
-    for (int t = lo; t < hi; ++t) {
-        const TP* row = proj + (size_t)t * ld + c;
-        const float z = sigmoid_f(to_f(row[z_off]) + bzc), u = to_f(row[x_off]) + bxc;
-        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-        Sv = (1.0f - z) * Sv + z * cand;
-        out[(size_t)t * ldo + c] = from_f<TO>(Sv * silu_f(to_f(row[g_off])));
+    for (int t = lo; t < hi; t += 8) {
+        float pz[8], px[8], pg[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const TP* row = proj + (size_t)min(t + i, hi - 1) * ld + c;
+            pz[i] = to_f(row[z_off]);
+            px[i] = to_f(row[x_off]);
+            pg[i] = to_f(row[g_off]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (t + i < hi) {
+                const float z = sigmoid_f(pz[i] + bzc), u = px[i] + bxc;
+                const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+                Sv = (1.0f - z) * Sv + z * cand;
+                out[(size_t)(t + i) * ldo + c] = from_f<TO>(Sv * silu_f(pg[i]));
+            }
+        }
     }
     if (hi == t1 && lo < hi) *st = Sv;
 }

@@ -164,7 +164,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_decay_linear_attention_chunked": [P, I, L, I, I, I, P, P, P, P, P, P, L, P, I, I, I, I, I, P],
         "aien_latent_prepare": [P, I, L, I, P, P, I, F, P, I, L, I, I, I, I, P, P, P, P, I, I, P],
         "aien_rotate_pairs_rows": [P, I, L, L, P, I, L, L, I, I, I, I, P, P, P],
-        "aien_latent_attention_tc": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
+        "aien_latent_attention_tc": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, P, P],
+        "aien_head_project_tc": [P, L, L, P, P, I, L, L, I, I, I, I, P],
         "aien_latent_attention_tc_supports": [I, I],
         "aien_head_project": [P, I, L, L, P, I, L, L, P, I, L, L, I, I, I, I, P],
         "aien_latent_attention": [P, L, P, I, P, I, P, P, P, P, I, L, I, I, I, I, I, I, F, P, P],
@@ -1295,6 +1296,9 @@ def gated_recurrence(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz:
 
 
 # ---------------------------------------------------------------------------- attention over a cached latent
+_LATENT_IMPL = __import__("os").environ.get("AIEN_B200_LATENT_ATTENTION", "tc").strip().lower()     # "tc" | "plain": pins the plain kernels
+
+
 def latent_prepare(d: torch.Tensor, q_rank: int, wq: Optional[torch.Tensor], eps: float, cq: Optional[torch.Tensor],
                    kv_off: int = 0, kv_rank: int = 0, rot_dim: int = 0, rot_dims: int = 0, wkv: Optional[torch.Tensor] = None,
                    cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
@@ -1338,13 +1342,20 @@ def rotate_pairs_rows(q: torch.Tensor, q_head: int, col0: int, out: torch.Tensor
 
 
 def head_project(a: torch.Tensor, a_head: int, a_col0: int, w: torch.Tensor, out: torch.Tensor, o_head: int, o_col0: int) -> None:
-    """out[t, h*o_head + o_col0 + n] = sum_k a[t, h*a_head + a_col0 + k] * w[h, n, k]: one product per head, w [heads, N, K]."""
+    """out[t, h*o_head + o_col0 + n] = sum_k a[t, h*a_head + a_col0 + k] * w[h, n, k]: one product per head, w [heads, N, K].
+    bfloat16 operands whose rows are whole aligned 16-byte pieces run on the tensor cores, everything else on the CUDA cores;
+    both sum in float32."""
     _dev(a, w, out)
     heads, N, K_ = w.shape
     M = a.shape[0]
     assert a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous() and out.shape[0] == M
     assert (heads - 1) * a_head + a_col0 + K_ <= a.shape[1] and (heads - 1) * o_head + o_col0 + N <= out.shape[1]
     av, ov = a[:, a_col0:], out[:, o_col0:]
+    if (_LATENT_IMPL != "plain" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K_ % 8 == 0 and a.stride(0) % 8 == 0
+            and a_head % 8 == 0 and av.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        _check(lib().aien_head_project_tc(_p(av), a.stride(0), int(a_head), _p(w), _p(ov), dt(out), out.stride(0), int(o_head), M, N, K_,
+                                          heads, _stream()), "head_project_tc")
+        return
     _check(lib().aien_head_project(_p(av), dt(a), a.stride(0), int(a_head), _p(w), dt(w), K_, N * K_, _p(ov), dt(out), out.stride(0),
                                    int(o_head), M, N, K_, heads, _stream()), "head_project")
 
@@ -1368,8 +1379,6 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
            "latent_attention")
 
 
-_LATENT_IMPL = __import__("os").environ.get("AIEN_B200_LATENT_ATTENTION", "tc").strip().lower()     # "tc" | "plain"
-
 
 def latent_attention_tc_supports(dtype: torch.dtype, kv_rank: int, rot_dim: int) -> bool:
     """Whether the tensor-core kernel takes this case: bfloat16, a latent of 64 / 128 / 256 / 512, a rotated part that is a multiple of 16."""
@@ -1378,10 +1387,13 @@ def latent_attention_tc_supports(dtype: torch.dtype, kv_rank: int, rot_dim: int)
 
 def latent_attention_tc(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, max_blocks: int, q_start: torch.Tensor,
                         positions: torch.Tensor, out: torch.Tensor, num_seqs: int, heads: int, kv_rank: int, rot_dim: int,
-                        page_size: int, window: int, scale: float, sinks: Optional[torch.Tensor]) -> None:
+                        page_size: int, window: int, scale: float, sinks: Optional[torch.Tensor], ksplit: int = 1,
+                        scratch: Optional[torch.Tensor] = None) -> None:
     """latent_attention on the tensor cores.  q bfloat16 [T, heads*(kv_rank + rot_dim)] and out bfloat16 [T, heads*kv_rank],
     both contiguous; the T tokens are the portions q_start[s]..q_start[s+1] of ``num_seqs`` requests (row s of the block
-    table), each portion's positions counting up from positions[q_start[s]]."""
+    table), each portion's positions counting up from positions[q_start[s]].  ``ksplit`` > 1 deals the key blocks of every
+    tile out to that many CTAs and merges their results in a second launch (steps with few tiles); ``scratch`` is then
+    float32 with ``latent_attention_tc_scratch(T, heads, kv_rank, ksplit)`` numbers."""
     _dev(q, cache, block_table, q_start, positions, out, sinks)
     T, D = q.shape[0], kv_rank + rot_dim
     assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -1389,6 +1401,29 @@ def latent_attention_tc(q: torch.Tensor, cache: torch.Tensor, block_table: torch
     assert q.shape[1] == heads * D and tuple(out.shape) == (T, heads * kv_rank)
     assert block_table.dtype == torch.int32 and q_start.dtype == torch.int32 and positions.dtype == torch.int32
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == heads)
+    part_o = part_ml = None
+    if ksplit > 1:
+        _dev(scratch)
+        n_o = T * heads * ksplit * kv_rank
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.is_contiguous()
+        assert scratch.numel() >= latent_attention_tc_scratch(T, heads, kv_rank, ksplit)
+        part_o, part_ml = scratch[:n_o], scratch[n_o:]
     _check(lib().aien_latent_attention_tc(_p(q), _p(cache), _p(block_table), int(max_blocks), _p(q_start), _p(positions), _p(out), T,
                                           int(num_seqs), int(heads), int(kv_rank), int(rot_dim), int(page_size), int(window),
-                                          float(scale), _p(sinks), _stream()), "latent_attention_tc")
+                                          float(scale), _p(sinks), int(ksplit), _p(part_o), _p(part_ml), _stream()), "latent_attention_tc")
+
+
+LATENT_TC_TILE = 64          # (token, head) rows and keys per tile of the tensor-core kernel
+
+
+def latent_attention_tc_scratch(num_tokens: int, heads: int, kv_rank: int, ksplit: int) -> int:
+    return num_tokens * heads * ksplit * (kv_rank + 2) if ksplit > 1 else 0
+
+
+def latent_attention_tc_ksplit(num_tokens: int, num_seqs: int, heads: int, max_ctx: int, window: int) -> int:
+    """Into how many CTAs the key blocks of a tile are dealt: enough to occupy the GPU (148 SMs, one CTA each, two rounds)
+    when the step has few tiles, never more than a tile has blocks.  Depends on the step's sizes only."""
+    tiles = (num_tokens * heads) // LATENT_TC_TILE + num_seqs
+    span = min(window, max_ctx) if window > 0 else max_ctx
+    blocks = max(1, (span + LATENT_TC_TILE - 1) // LATENT_TC_TILE + 1)
+    return max(1, min(blocks, 296 // tiles)) if tiles <= 148 else 1

@@ -86,7 +86,9 @@ class LatentAttention(Mixer):
         n = self.num_heads
         per_token = (self.q_rank + self.row) * 4 + self.q_rank * lim.itemsize + n * self.q_head * 4 + n * self.row * 4 \
             + n * self.kv_rank * lim.itemsize + n * self.value_dim * lim.itemsize + self.hidden_size * 4
-        return lim.max_tokens * per_token + 16384
+        # the partial results of a step with few tiles: at most 296 CTAs' worth of 64 rows each
+        split = 296 * K.LATENT_TC_TILE * (self.kv_rank + 2) * 4 + (lim.max_seqs + 1) * n * 296 * (self.kv_rank + 2) * 4 // 64
+        return lim.max_tokens * per_token + 16384 + split
 
     # ---- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
@@ -103,16 +105,19 @@ class LatentAttention(Mixer):
         cq = ws.take((T, self.q_rank), ctx.dtype)
         K.latent_prepare(d, self.q_rank, self.dq_norm, self.norm_eps, cq, self.q_rank, self.kv_rank, self.rot_dim, rdims,
                          self.dkv_norm, cos, sin, group.slot_map if writes else None, cache if writes else None)
-        q = linear(ctx, cq, self.w_uq, out_dtype=torch.float32)         # per head: unrotated | rotated part, before rotation
         tc = K.latent_attention_tc_supports(cache.dtype, self.kv_rank, self.rot_dim) and ctx.dtype == torch.bfloat16
+        # per head: unrotated | rotated part, before rotation; an operand of the tensor-core products where those run
+        q = linear(ctx, cq, self.w_uq, out_dtype=torch.bfloat16 if tc else torch.float32)
         qf = ws.take((T, n * self.row), torch.bfloat16 if tc else torch.float32)    # per head: the query in the latent | rotated part
         K.head_project(q, self.q_head, 0, self.w_uk_t, qf, self.row, 0)
         if self.rot_dim:
             K.rotate_pairs_rows(q, self.q_head, self.head_dim, qf, self.row, self.kv_rank, n, self.rot_dim, rdims, cos, sin)
         mixed = ws.take((T, n * self.kv_rank), ctx.dtype)
         if tc:
+            ksplit = K.latent_attention_tc_ksplit(T, ctx.num_seqs, n, ctx.max_ctx_len, self.window)
+            scratch = ws.take((K.latent_attention_tc_scratch(T, n, self.kv_rank, ksplit),), torch.float32) if ksplit > 1 else None
             K.latent_attention_tc(qf, cache, group.block_table, group.max_blocks, ctx.q_start, ctx.positions, mixed, ctx.num_seqs, n,
-                                  self.kv_rank, self.rot_dim, group.page_size, self.window, self.scale, self.sinks)
+                                  self.kv_rank, self.rot_dim, group.page_size, self.window, self.scale, self.sinks, ksplit, scratch)
         else:
             K.latent_attention(qf, cache, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, mixed, n, self.kv_rank,
                                self.rot_dim, group.page_size, self.window, self.scale, self.sinks)
