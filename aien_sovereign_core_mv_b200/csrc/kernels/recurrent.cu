@@ -112,6 +112,59 @@ decay_linear_attention_kernel(const TP* __restrict__ proj, long ld, int q_off, i
     }
 }
 
+// The recurrence itself for requests that bring one token each: the state streams through once.  One CTA per (request,
+// head, 32 value columns); thread (v, g) walks the rows d = g, g + 8, ... of its column: S[d][v] = lambda S[d][v] + k[d] v[v],
+// o[v] += S[d][v] q[d]; the eight row groups of a column are added through shared memory in order.
+template <typename TP>
+__global__ void __launch_bounds__(256)
+decay_linear_attention_token_kernel(const TP* __restrict__ proj, long ld, int q_off, int k_off, int v_off,
+                                    const float* __restrict__ decay, float* __restrict__ state,
+                                    const int* __restrict__ slot_map, const int* __restrict__ q_start,
+                                    const int* __restrict__ positions, float* __restrict__ out, long ldo,
+                                    int H, int dim, int vd) {
+    extern __shared__ float sm[];
+    float* qs = sm;                 // [dim]
+    float* ks = qs + dim;           // [dim]
+    __shared__ float part[8][33];
+    const int s = blockIdx.x, h = blockIdx.y, v = blockIdx.z * 32 + (threadIdx.x & 31), grp = threadIdx.x >> 5;
+    const int t = q_start[s];
+    const TP* row = proj + (size_t)t * ld;
+    for (int d = threadIdx.x; d < dim; d += 256) {
+        qs[d] = silu_f(to_f(row[q_off + (size_t)h * dim + d]));
+        ks[d] = silu_f(to_f(row[k_off + (size_t)h * dim + d]));
+    }
+    __syncthreads();
+    float acc = 0.f;
+    if (v < vd) {
+        const float lam = decay[h];
+        const bool fresh = positions[t] == 0;
+        const float vv = silu_f(to_f(row[v_off + (size_t)h * vd + v]));
+        float* st = state + (((size_t)slot_map[s] * H + h) * dim) * vd + v;
+        for (int d0 = grp; d0 < dim; d0 += 32) {                           // four rows' loads in flight
+            float sv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sv[i] = (!fresh && d0 + 8 * i < dim) ? st[(size_t)(d0 + 8 * i) * vd] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int d = d0 + 8 * i;
+                if (d < dim) {
+                    const float n = fmaf(lam, sv[i], ks[d] * vv);
+                    st[(size_t)d * vd] = n;
+                    acc = fmaf(n, qs[d], acc);
+                }
+            }
+        }
+    }
+    part[grp][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (grp == 0 && v < vd) {
+        float o = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) o += part[g][threadIdx.x];
+        out[(size_t)t * ldo + (size_t)h * vd + v] = o;
+    }
+}
+
 // ---------------------------------------------------------------- the same, chunks side by side
 // For portions of prompts the chunks of a request need not wait for one another.  Three launches:
 //   1. every chunk's own contribution to the state   U_c = sum_j lambda^(n-1-j) k_j v_j^T        (chunks in parallel)
@@ -490,9 +543,14 @@ static size_t la_smem_bytes(int dim) {
 }
 
 template <typename TP>
-static int launch_decay_linear_attention(dim3 grid, size_t smem, cudaStream_t stream, const TP* proj, long ld, int q_off, int k_off,
+static int launch_decay_linear_attention(int single_tokens, dim3 grid, size_t smem, cudaStream_t stream, const TP* proj, long ld, int q_off, int k_off,
                                          int v_off, const float* decay, float* state, const int* slot_map, const int* q_start,
                                          const int* positions, float* out, long ldo, int H, int dim, int vd) {
+    if (single_tokens) {
+        decay_linear_attention_token_kernel<TP><<<dim3(grid.x, grid.y, (vd + 31) / 32), 256, 2 * dim * sizeof(float), stream>>>(
+            proj, ld, q_off, k_off, v_off, decay, state, slot_map, q_start, positions, out, ldo, H, dim, vd);
+        return 0;
+    }
     auto kern = decay_linear_attention_kernel<TP>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return AIEN_E_STATE;
@@ -502,10 +560,11 @@ static int launch_decay_linear_attention(dim3 grid, size_t smem, cudaStream_t st
 
 // proj [T, ld]: the projections before their silu, q at column q_off (H*dim), k at k_off, v at v_off (H*vd).
 // decay float32 [H]; state float32 [slots, H, dim, vd]; out float32 [T, ldo] receives o (H*vd per token).
+// single_tokens != 0: every request of the step brings exactly one token (the state streams through once).
 AIEN_API int aien_decay_linear_attention(const void* proj, int p_dt, long ld, int q_off, int k_off, int v_off,
                                          const float* decay, float* state, const int* slot_map, const int* q_start,
                                          const int* positions, float* out, long ldo, int S, int H, int dim, int vd,
-                                         cudaStream_t stream) {
+                                         int single_tokens, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (H <= 0 || dim <= 0 || vd <= 0 || H > 65535) return AIEN_E_SHAPE;
     const size_t smem = la_smem_bytes(dim);
@@ -513,7 +572,7 @@ AIEN_API int aien_decay_linear_attention(const void* proj, int p_dt, long ld, in
     dim3 grid(S, H, (vd + LA_VS - 1) / LA_VS);
     if (grid.z > 65535) return AIEN_E_SHAPE;
     int rc = 0;
-    AIEN_DISPATCH_DTYPE(p_dt, TP, (rc = launch_decay_linear_attention<TP>(grid, smem, stream, (const TP*)proj, ld, q_off, k_off, v_off, decay,
+    AIEN_DISPATCH_DTYPE(p_dt, TP, (rc = launch_decay_linear_attention<TP>(single_tokens, grid, smem, stream, (const TP*)proj, ld, q_off, k_off, v_off, decay,
                                                                           state, slot_map, q_start, positions, out, ldo, H, dim, vd)));
     if (rc != 0) return rc;
     return launch_status();

@@ -158,7 +158,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
         "aien_attention_decode_stream_error": [],
         "aien_collect_wait_errors": [P, P],
-        "aien_decay_linear_attention": [P, I, L, I, I, I, P, P, P, P, P, P, L, I, I, I, I, P],
+        "aien_decay_linear_attention": [P, I, L, I, I, I, P, P, P, P, P, P, L, I, I, I, I, I, P],
         "aien_gated_rmsnorm": [P, L, P, I, L, P, I, F, P, I, L, I, I, P],
         "aien_gated_recurrence": [P, I, L, I, I, I, P, P, I, P, P, P, P, P, I, L, I, I, I, P],
         "aien_decay_linear_attention_chunked": [P, I, L, I, I, I, P, P, P, P, P, P, L, P, I, I, I, I, I, P],
@@ -1229,13 +1229,15 @@ def softcap(v: torch.Tensor, cap: float) -> None:
 # ---------------------------------------------------------------------------- mixers with a state of fixed size
 def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
                            slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
-                           num_seqs: int, heads: int, dim: int, vdim: int, scratch: Optional[torch.Tensor] = None) -> None:
+                           num_seqs: int, heads: int, dim: int, vdim: int, scratch: Optional[torch.Tensor] = None,
+                           single_tokens: bool = False) -> None:
     """Per head S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v = silu of the columns of ``proj`` [T, *]
     at q_off (heads*dim), k_off (heads*dim), v_off (heads*vdim).  ``state`` float32 [slots, heads, dim, vdim]: request s
     of the step (tokens q_start[s]..q_start[s+1]) continues from slot slot_map[s], from zero when its first token has
     position 0, and leaves its state there.  ``out`` float32 [T, heads*vdim].  With ``scratch`` (float32,
     ``decay_linear_attention_scratch(T, num_seqs, ...)`` numbers) the chunks of a portion run side by side in three
-    launches (for portions of prompts); without it one CTA walks a portion's chunks in order (single tokens)."""
+    launches (for portions of prompts); without it one CTA walks a portion's chunks in order.  ``single_tokens``: every
+    request brings exactly one token, and the state streams through a kernel made for that."""
     _dev(proj, decay, state, slot_map, q_start, positions, out)
     assert proj.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == heads * vdim
     assert decay.dtype == torch.float32 and decay.numel() == heads and decay.is_contiguous()
@@ -1254,7 +1256,8 @@ def decay_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: in
         return
     _check(lib().aien_decay_linear_attention(_p(proj), dt(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _p(decay),
                                              _p(state), _p(slot_map), _p(q_start), _p(positions), _p(out), out.stride(0),
-                                             int(num_seqs), int(heads), int(dim), int(vdim), _stream()), "decay_linear_attention")
+                                             int(num_seqs), int(heads), int(dim), int(vdim), 1 if single_tokens else 0, _stream()),
+           "decay_linear_attention")
 
 
 def decay_linear_attention_scratch(num_tokens: int, num_seqs: int, heads: int, dim: int, vdim: int) -> int:

@@ -63,7 +63,7 @@ class DecayLinearAttention(Mixer):
             n = K.decay_linear_attention_scratch(T, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim)
             scratch = ctx.workspace.take((n,), torch.float32)
         K.decay_linear_attention(proj, 0, self.qk_dim, 2 * self.qk_dim, self.decay, state, group.slot_map, ctx.q_start, ctx.positions,
-                                 o, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim, scratch)
+                                 o, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim, scratch, single_tokens=ctx.decode_only)
         y = ctx.workspace.take((T, self.v_dim), ctx.dtype)
         K.gated_rmsnorm(o, proj[:, 2 * self.qk_dim + self.v_dim:], self.norm_w, self.norm_eps, y)
         return linear(ctx, y, self.w_o, out_dtype=torch.float32)

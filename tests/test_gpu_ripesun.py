@@ -215,6 +215,17 @@ def test_decayed_linear_attention_in_one_step_and_in_pieces(heads, dim, vdim, de
         at += n
     H.assert_close(np.concatenate(got), want0, 2e-5, "the same tokens in pieces")
     H.assert_close(st[1, 0].cpu().numpy(), S0, 2e-5, "state after the pieces")
+    # both requests once more, token by token in steps of two single tokens (the kernel made for such steps), slots swapped
+    got0, got1 = [], []
+    for i in range(lens[1]):
+        rows = torch.cat([proj[i:i + 1], proj[lens[0] + i:lens[0] + i + 1]]).contiguous()
+        o = torch.zeros(2, heads * vdim, dtype=torch.float32).cuda()
+        K.decay_linear_attention(rows, 0, heads * dim, 2 * heads * dim, dec, st[1], i32([1, 2]), i32([0, 1, 2]), i32([i, i]), o, 2,
+                                 heads, dim, vdim, single_tokens=True)
+        got0.append(o[0].cpu().numpy()); got1.append(o[1].cpu().numpy())
+    H.assert_close(np.stack(got0), want0[:lens[1]], 2e-5, "single tokens, first request")
+    H.assert_close(np.stack(got1), want1, 2e-5, "single tokens, second request")
+    H.assert_close(st[1, 2].cpu().numpy(), S1, 2e-5, "state after single tokens")
 
 
 @pytest.mark.parametrize("segments", [False, True])
