@@ -26,6 +26,9 @@ __device__ __forceinline__ void lx_cp_async_wait_all() { asm volatile("cp.async.
 __device__ __forceinline__ void lx_ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
+__device__ __forceinline__ void lx_ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
 __device__ __forceinline__ void lx_ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
@@ -39,20 +42,25 @@ __device__ __forceinline__ uint32_t lx_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&p);
 }
 
-template <int R>
-__global__ void __launch_bounds__(LX_THREADS, 1)
+// SLABS: 16-row slabs of a tile (4: tiles of 64 rows, for portions; 1: tiles of 16 rows, for steps of single tokens, where
+// a request has only its heads as rows).  The 8 / SLABS warps of a slab deal out the keys of a block for the scores and
+// the channels for the weighted sum.
+template <int R, int SLABS>
+__global__ void __launch_bounds__(LX_THREADS, SLABS == 1 ? 2 : 1)
 latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                            const int* __restrict__ positions, int S, __nv_bfloat16* __restrict__ out,
                            int H, int rd, int page_size, int window, float scale_log2e, const float* __restrict__ sinks,
                            int ksplit, float* __restrict__ part_o, float* __restrict__ part_ml) {
-    constexpr int DT = R / 16;                   // n8 tiles of this warp's half of the channels
+    constexpr int BM = SLABS * 16, PARTS = 8 / SLABS, KP = LX_BN / PARTS, NJ = KP / 8, CHP = R / PARTS;
+    constexpr int DT = CHP / 8;                  // n8 tiles of this warp's share of the channels
+    static_assert(DT >= 2 && DT % 2 == 0, "a warp's share of the latent must be whole pairs of n8 tiles");
     const int D = R + rd, STR = D + 8, CH = D / 8, KS = D / 16;
     extern __shared__ __align__(16) uint8_t lx_smem[];
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lx_smem);          // [64][STR]
-    __nv_bfloat16* Ks = Qs + LX_BM * STR;                                   // [64][STR]
-    __nv_bfloat16* Ps = Ks + LX_BN * STR;                                   // [64][LX_PSTR]
-    float* stat = reinterpret_cast<float*>(Ps + LX_BM * LX_PSTR);           // [2][64]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lx_smem);          // [BM][STR]
+    __nv_bfloat16* Ks = Qs + BM * STR;                                      // [64][STR]
+    __nv_bfloat16* Ps = Ks + LX_BN * STR;                                   // [BM][LX_PSTR]
+    float* stat = reinterpret_cast<float*>(Ps + BM * LX_PSTR);              // [PARTS][BM]
     __shared__ int key_there[LX_BN];                                        // whether the block's key is in the cache and needed
     const uint32_t Qs_u = (uint32_t)__cvta_generic_to_shared(Qs), Ks_u = (uint32_t)__cvta_generic_to_shared(Ks);
     const uint32_t Ps_u = (uint32_t)__cvta_generic_to_shared(Ps);
@@ -60,28 +68,28 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     // which request, which rows
     int s = -1, row0 = 0, acc = 0;
     for (int i = 0; i < S; ++i) {
-        const int tiles = ((q_start[i + 1] - q_start[i]) * H + LX_BM - 1) / LX_BM;
+        const int tiles = ((q_start[i + 1] - q_start[i]) * H + BM - 1) / BM;
         if ((int)blockIdx.x < acc + tiles) {
             s = i;
-            row0 = ((int)blockIdx.x - acc) * LX_BM;
+            row0 = ((int)blockIdx.x - acc) * BM;
             break;
         }
         acc += tiles;
     }
     if (s < 0) return;
     const int qs = q_start[s], len = q_start[s + 1] - qs;
-    const int nrows = min(LX_BM, len * H - row0);
+    const int nrows = min(BM, len * H - row0);
     const int pos_first = positions[qs];
     const int pos_lo = pos_first + row0 / H, pos_hi = pos_first + (row0 + nrows - 1) / H;
     const int first = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
     const int* bt = block_table + (size_t)s * max_blocks;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int slab = warp & 3, half = warp >> 2;
+    const int slab = warp % SLABS, half = warp / SLABS;                     // half: which share of the keys / channels
     const int g = lane >> 2, c = lane & 3;
 
     const __nv_bfloat16* qbase = q + ((size_t)qs * H + row0) * D;
-    for (int idx = tid; idx < LX_BM * CH; idx += LX_THREADS) {
+    for (int idx = tid; idx < BM * CH; idx += LX_THREADS) {
         const int r = idx / CH, ch = idx - r * CH;
         const bool valid = r < nrows;
         lx_cp_async16(Qs_u + (uint32_t)(r * STR + ch * 8) * 2, qbase + (size_t)(valid ? r : 0) * D + ch * 8, valid);
@@ -123,31 +131,39 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         lx_cp_async_wait_all();
         __syncthreads();                                                   // the block's rows (and, first time, Q) have landed
 
-        float sc[4][4];
+        float sc[NJ][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+        for (int j = 0; j < NJ; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
         if (active) {
+#pragma unroll 4
             for (int kk = 0; kk < KS; ++kk) {
                 uint32_t q0r, q1r, q2r, q3r;
                 lx_ldmatrix_x4(q_frag_u + kk * 32, q0r, q1r, q2r, q3r);
+                if constexpr (NJ == 1) {
+                    const int row = half * KP + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
+                    uint32_t b0, b1;
+                    lx_ldmatrix_x2(Ks_u + (uint32_t)(row * STR + col) * 2, b0, b1);
+                    lx_mma(sc[0], q0r, q1r, q2r, q3r, b0, b1);
+                } else {
 #pragma unroll
-                for (int j = 0; j < 4; j += 2) {
-                    const int mi = lane >> 3;
-                    const int row = half * 32 + (j + (mi >> 1)) * 8 + (lane & 7), col = kk * 16 + (mi & 1) * 8;
-                    uint32_t b0, b1, b2, b3;
-                    lx_ldmatrix_x4(Ks_u + (uint32_t)(row * STR + col) * 2, b0, b1, b2, b3);
-                    lx_mma(sc[j], q0r, q1r, q2r, q3r, b0, b1);
-                    lx_mma(sc[j + 1], q0r, q1r, q2r, q3r, b2, b3);
+                    for (int j = 0; j < NJ; j += 2) {
+                        const int mi = lane >> 3;
+                        const int row = half * KP + (j + (mi >> 1)) * 8 + (lane & 7), col = kk * 16 + (mi & 1) * 8;
+                        uint32_t b0, b1, b2, b3;
+                        lx_ldmatrix_x4(Ks_u + (uint32_t)(row * STR + col) * 2, b0, b1, b2, b3);
+                        lx_mma(sc[j], q0r, q1r, q2r, q3r, b0, b1);
+                        lx_mma(sc[j + (NJ > 1 ? 1 : 0)], q0r, q1r, q2r, q3r, b2, b3);
+                    }
                 }
             }
         }
         // masks and this half's row maxima (scores in log2 units)
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NJ; ++j) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int kl = half * 32 + j * 8 + 2 * c + e, key = kb * LX_BN + kl;
+                const int kl = half * KP + j * 8 + 2 * c + e, key = kb * LX_BN + kl;
                 const bool there = key_there[kl] != 0;
                 const bool ok0 = there && key <= qpos0 && key >= wlo0, ok1 = there && key <= qpos1 && key >= wlo1;
                 sc[j][e] = ok0 ? sc[j][e] * scale_log2e : -INFINITY;
@@ -159,24 +175,27 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         if (c == 0) {
-            stat[half * LX_BM + ra] = mx0;
-            stat[half * LX_BM + rb] = mx1;
+            stat[half * BM + ra] = mx0;
+            stat[half * BM + rb] = mx1;
         }
-        __syncthreads();                                                   // both halves' maxima are there
-        mx0 = fmaxf(mx0, stat[(half ^ 1) * LX_BM + ra]);
-        mx1 = fmaxf(mx1, stat[(half ^ 1) * LX_BM + rb]);
+        __syncthreads();                                                   // every share's maxima are there
+#pragma unroll
+        for (int pp = 0; pp < PARTS; ++pp) {
+            mx0 = fmaxf(mx0, stat[pp * BM + ra]);
+            mx1 = fmaxf(mx1, stat[pp * BM + rb]);
+        }
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         const float corr0 = (m_run[0] == -INFINITY) ? 0.f : exp2f(m_run[0] - mn0);
         const float corr1 = (m_run[1] == -INFINITY) ? 0.f : exp2f(m_run[1] - mn1);
         const float base0 = (mn0 == -INFINITY) ? 0.f : mn0, base1 = (mn1 == -INFINITY) ? 0.f : mn1;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             float p00 = exp2f(sc[j][0] - base0), p01 = exp2f(sc[j][1] - base0);      // exp2(-inf) = 0 for masked keys
             float p10 = exp2f(sc[j][2] - base1), p11 = exp2f(sc[j][3] - base1);
             sum0 += p00 + p01;
             sum1 += p10 + p11;
-            const int col = half * 32 + j * 8 + 2 * c;
+            const int col = half * KP + j * 8 + 2 * c;
             *reinterpret_cast<uint32_t*>(Ps + ra * LX_PSTR + col) = lx_pack(p00, p01);
             *reinterpret_cast<uint32_t*>(Ps + rb * LX_PSTR + col) = lx_pack(p10, p11);
         }
@@ -186,7 +205,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         m_run[1] = mn1;
 #pragma unroll
         for (int d = 0; d < DT; ++d) { o[d][0] *= corr0; o[d][1] *= corr0; o[d][2] *= corr1; o[d][3] *= corr1; }
-        __syncthreads();                                                   // the probabilities of both halves are there
+        __syncthreads();                                                   // the probabilities of every share are there
         if (active) {
 #pragma unroll
             for (int ks = 0; ks < LX_BN / 16; ++ks) {
@@ -194,7 +213,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                 lx_ldmatrix_x4(p_frag_u + ks * 32, a0, a1, a2, a3);
 #pragma unroll
                 for (int d = 0; d < DT; d += 2) {
-                    const int row = ks * 16 + (lane & 15), col = half * (R / 2) + (d + (lane >> 4)) * 8;
+                    const int row = ks * 16 + (lane & 15), col = half * CHP + (d + (lane >> 4)) * 8;
                     uint32_t b0, b1, b2, b3;
                     lx_ldmatrix_x4_trans(Ks_u + (uint32_t)(row * STR + col) * 2, b0, b1, b2, b3);
                     lx_mma(o[d], a0, a1, a2, a3, b0, b1);
@@ -211,12 +230,16 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
         l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1); l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
         if (c == 0) {
-            stat[half * LX_BM + ra] = l_run[0];
-            stat[half * LX_BM + rb] = l_run[1];
+            stat[half * BM + ra] = l_run[0];
+            stat[half * BM + rb] = l_run[1];
         }
         __syncthreads();
-        l_run[0] += stat[(half ^ 1) * LX_BM + ra];
-        l_run[1] += stat[(half ^ 1) * LX_BM + rb];
+        l_run[0] = l_run[1] = 0.f;
+#pragma unroll
+        for (int pp = 0; pp < PARTS; ++pp) {
+            l_run[0] += stat[pp * BM + ra];
+            l_run[1] += stat[pp * BM + rb];
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int row = r == 0 ? ra : rb;
@@ -226,7 +249,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
                 part_ml[slot * 2] = m_run[r];
                 part_ml[slot * 2 + 1] = l_run[r];
             }
-            float* dst = part_o + slot * R + half * (R / 2);
+            float* dst = part_o + slot * R + half * CHP;
 #pragma unroll
             for (int d = 0; d < DT; ++d) *reinterpret_cast<float2*>(dst + d * 8 + 2 * c) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
         }
@@ -236,12 +259,16 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1); l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
     if (c == 0) {
-        stat[half * LX_BM + ra] = l_run[0];
-        stat[half * LX_BM + rb] = l_run[1];
+        stat[half * BM + ra] = l_run[0];
+        stat[half * BM + rb] = l_run[1];
     }
     __syncthreads();
-    l_run[0] += stat[(half ^ 1) * LX_BM + ra];
-    l_run[1] += stat[(half ^ 1) * LX_BM + rb];
+    l_run[0] = l_run[1] = 0.f;
+#pragma unroll
+    for (int pp = 0; pp < PARTS; ++pp) {
+        l_run[0] += stat[pp * BM + ra];
+        l_run[1] += stat[pp * BM + rb];
+    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = r == 0 ? ra : rb;
@@ -254,7 +281,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
             l_run[r] = l_run[r] * corr + exp2f(sk - mn);
         }
         const float inv = l_run[r] > 0.f ? corr / l_run[r] : 0.f;
-        __nv_bfloat16* dst = out + ((size_t)qs * H + row0 + row) * R + half * (R / 2);
+        __nv_bfloat16* dst = out + ((size_t)qs * H + row0 + row) * R + half * CHP;
 #pragma unroll
         for (int d = 0; d < DT; ++d)
             *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * c) = lx_pack(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
@@ -285,16 +312,17 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
     }
 }
 
-template <int R>
+template <int R, int SLABS>
 static int launch_latent_tc(const void* q, const void* cache, const int* bt, int max_blocks, const int* q_start, const int* positions,
                             int T, int S, void* out, int H, int rd, int page_size, int window, float scale, const float* sinks,
                             int ksplit, float* part_o, float* part_ml, cudaStream_t stream) {
     const int D = R + rd;
-    const size_t smem = (size_t)(LX_BM + LX_BN) * (D + 8) * 2 + (size_t)LX_BM * LX_PSTR * 2 + 2 * LX_BM * sizeof(float);
+    constexpr int BM = SLABS * 16;
+    const size_t smem = (size_t)(BM + LX_BN) * (D + 8) * 2 + (size_t)BM * LX_PSTR * 2 + 8 * 16 * sizeof(float);
     if (smem > 227 * 1024) return AIEN_E_SHAPE;
-    auto kern = latent_attention_tc_kernel<R>;
+    auto kern = latent_attention_tc_kernel<R, SLABS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
-    const long tiles = ((long)T * H) / LX_BM + S;
+    const long tiles = ((long)T * H) / BM + S;
     kern<<<dim3((unsigned)tiles, ksplit), LX_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, max_blocks, q_start,
                                                                      positions, S, (__nv_bfloat16*)out, H, rd, page_size, window,
                                                                      scale * 1.4426950408889634f, sinks, ksplit, part_o, part_ml);
@@ -384,19 +412,23 @@ AIEN_API int aien_latent_attention_tc_supports(int kv_rank, int rot_dim) {
 // The step's T tokens are the portions q_start[s] .. q_start[s + 1] of S requests; positions[t] is token t's position.
 // ksplit > 1: the key blocks of every tile are dealt out to ksplit CTAs (for steps with few tiles); part_o (float32,
 // T * H * ksplit * kv_rank) and part_ml (float32, T * H * ksplit * 2) hold their partial results for the merging launch.
+// small_tiles != 0: tiles of 16 rows instead of 64 (steps in which every request brings one token), for latents of 128 and more.
 AIEN_API int aien_latent_attention_tc(const void* q, const void* cache, const int* block_table, int max_blocks, const int* q_start,
                                       const int* positions, void* out, int T, int S, int H, int kv_rank, int rot_dim, int page_size,
                                       int window, float scale, const float* sinks, int ksplit, float* part_o, float* part_ml,
-                                      cudaStream_t stream) {
+                                      int small_tiles, cudaStream_t stream) {
     if (T <= 0 || S <= 0) return 0;
     if (H <= 0 || page_size <= 0 || window < 0 || !aien_latent_attention_tc_supports(kv_rank, rot_dim)) return AIEN_E_SHAPE;
     if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 3)) return AIEN_E_ALIGN;
     if (ksplit < 1 || ksplit > 65535 || (ksplit > 1 && (part_o == nullptr || part_ml == nullptr || ((uintptr_t)part_o & 7)))) return AIEN_E_SHAPE;
-#define LX_CASE(RV)                                                                                                              \
+#define LX_CASE(RV, SL)                                                                                                          \
     if (kv_rank == RV)                                                                                                           \
-        return launch_latent_tc<RV>(q, cache, block_table, max_blocks, q_start, positions, T, S, out, H, rot_dim, page_size, window, \
-                                    scale, sinks, ksplit, part_o, part_ml, stream);
-    LX_CASE(64) LX_CASE(128) LX_CASE(256) LX_CASE(512)
+        return launch_latent_tc<RV, SL>(q, cache, block_table, max_blocks, q_start, positions, T, S, out, H, rot_dim, page_size,  \
+                                        window, scale, sinks, ksplit, part_o, part_ml, stream);
+    if (small_tiles && kv_rank >= 128) {                   // tiles of 16 rows: a latent of 64 would leave a warp half a pair of n8 tiles
+        LX_CASE(128, 1) LX_CASE(256, 1) LX_CASE(512, 1)
+    }
+    LX_CASE(64, 4) LX_CASE(128, 4) LX_CASE(256, 4) LX_CASE(512, 4)
 #undef LX_CASE
     return AIEN_E_SHAPE;
 }

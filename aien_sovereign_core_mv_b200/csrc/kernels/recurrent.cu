@@ -296,16 +296,28 @@ la_chunk_output_kernel(const TP* __restrict__ proj, long ld, int q_off, int k_of
     if (!la_locate(q_start, S, c, s, t0, n)) return;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const float l2 = log2f(decay[h]);
-    for (int idx = tid; idx < LC * dim; idx += 256) {
-        const int j = idx / dim, d = idx % dim;
-        float qv = 0.f, kv = 0.f;
-        if (j < n) {
-            const TP* row = proj + (size_t)(t0 + j) * ld + (size_t)h * dim + d;
-            qv = silu_f(to_f(row[q_off]));
-            kv = silu_f(to_f(row[k_off]));
+    for (int i0 = tid; i0 < LC * dim; i0 += 256 * 8) {                   // eight rows' loads in flight, then their silu and the transposed stores
+        float qv[8], kv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = i0 + u * 256;
+            const int j = idx / dim, d = idx % dim;
+            qv[u] = kv[u] = 0.f;
+            if (idx < LC * dim && j < n) {
+                const TP* row = proj + (size_t)(t0 + j) * ld + (size_t)h * dim + d;
+                qv[u] = to_f(row[q_off]);
+                kv[u] = to_f(row[k_off]);
+            }
         }
-        Qt[d * LPAD + j] = qv;
-        Kt[d * LPAD + j] = kv;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int idx = i0 + u * 256;
+            if (idx < LC * dim) {
+                const int j = idx / dim, d = idx % dim;
+                Qt[d * LPAD + j] = j < n ? silu_f(qv[u]) : 0.f;
+                Kt[d * LPAD + j] = j < n ? silu_f(kv[u]) : 0.f;
+            }
+        }
     }
     for (int idx = tid; idx < LC * LVT; idx += 256) {
         const int j = idx / LVT, v = idx % LVT;
@@ -358,6 +370,7 @@ la_chunk_output_kernel(const TP* __restrict__ proj, long ld, int q_off, int k_of
     {
         const float* p = P + ((size_t)c * H + h) * dim * vd + v0;
         const bool vec = (vd & 3) == 0;
+#pragma unroll 4
         for (int idx = tid; idx < dim * (LVT / 4); idx += 256) {
             const int d = idx / (LVT / 4), v4i = (idx % (LVT / 4)) * 4;
             float4 pp = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -164,7 +164,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_decay_linear_attention_chunked": [P, I, L, I, I, I, P, P, P, P, P, P, L, P, I, I, I, I, I, P],
         "aien_latent_prepare": [P, I, L, I, P, P, I, F, P, I, L, I, I, I, I, P, P, P, P, I, I, P],
         "aien_rotate_pairs_rows": [P, I, L, L, P, I, L, L, I, I, I, I, P, P, P],
-        "aien_latent_attention_tc": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, P, P],
+        "aien_latent_attention_tc": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, P, P, I, P],
         "aien_head_project_tc": [P, L, L, P, P, I, L, L, I, I, I, I, P],
         "aien_latent_attention_tc_supports": [I, I],
         "aien_head_project": [P, I, L, L, P, I, L, L, P, I, L, L, I, I, I, I, P],
@@ -1391,12 +1391,13 @@ def latent_attention_tc_supports(dtype: torch.dtype, kv_rank: int, rot_dim: int)
 def latent_attention_tc(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, max_blocks: int, q_start: torch.Tensor,
                         positions: torch.Tensor, out: torch.Tensor, num_seqs: int, heads: int, kv_rank: int, rot_dim: int,
                         page_size: int, window: int, scale: float, sinks: Optional[torch.Tensor], ksplit: int = 1,
-                        scratch: Optional[torch.Tensor] = None) -> None:
+                        scratch: Optional[torch.Tensor] = None, small_tiles: bool = False) -> None:
     """latent_attention on the tensor cores.  q bfloat16 [T, heads*(kv_rank + rot_dim)] and out bfloat16 [T, heads*kv_rank],
     both contiguous; the T tokens are the portions q_start[s]..q_start[s+1] of ``num_seqs`` requests (row s of the block
     table), each portion's positions counting up from positions[q_start[s]].  ``ksplit`` > 1 deals the key blocks of every
     tile out to that many CTAs and merges their results in a second launch (steps with few tiles); ``scratch`` is then
-    float32 with ``latent_attention_tc_scratch(T, heads, kv_rank, ksplit)`` numbers."""
+    float32 with ``latent_attention_tc_scratch(T, heads, kv_rank, ksplit)`` numbers.  ``small_tiles``: tiles of 16 rows
+    instead of 64, for steps in which every request brings one token (latents of 128 and more)."""
     _dev(q, cache, block_table, q_start, positions, out, sinks)
     T, D = q.shape[0], kv_rank + rot_dim
     assert q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -1413,7 +1414,8 @@ def latent_attention_tc(q: torch.Tensor, cache: torch.Tensor, block_table: torch
         part_o, part_ml = scratch[:n_o], scratch[n_o:]
     _check(lib().aien_latent_attention_tc(_p(q), _p(cache), _p(block_table), int(max_blocks), _p(q_start), _p(positions), _p(out), T,
                                           int(num_seqs), int(heads), int(kv_rank), int(rot_dim), int(page_size), int(window),
-                                          float(scale), _p(sinks), int(ksplit), _p(part_o), _p(part_ml), _stream()), "latent_attention_tc")
+                                          float(scale), _p(sinks), int(ksplit), _p(part_o), _p(part_ml), 1 if small_tiles else 0, _stream()),
+           "latent_attention_tc")
 
 
 LATENT_TC_TILE = 64          # (token, head) rows and keys per tile of the tensor-core kernel
@@ -1423,10 +1425,15 @@ def latent_attention_tc_scratch(num_tokens: int, heads: int, kv_rank: int, kspli
     return num_tokens * heads * ksplit * (kv_rank + 2) if ksplit > 1 else 0
 
 
-def latent_attention_tc_ksplit(num_tokens: int, num_seqs: int, heads: int, max_ctx: int, window: int) -> int:
-    """Into how many CTAs the key blocks of a tile are dealt: enough to occupy the GPU (148 SMs, one CTA each, two rounds)
+def latent_attention_tc_small_tiles(decode_only: bool, kv_rank: int) -> bool:
+    """Whether a step takes the tiles of 16 rows: every request brings one token, and the latent is wide enough."""
+    return bool(decode_only) and kv_rank >= 128
+
+
+def latent_attention_tc_ksplit(num_tokens: int, num_seqs: int, heads: int, max_ctx: int, window: int, small_tiles: bool = False) -> int:
+    """Into how many CTAs the key blocks of a tile are dealt: enough to occupy the GPU (148 SMs, two rounds of CTAs)
     when the step has few tiles, never more than a tile has blocks.  Depends on the step's sizes only."""
-    tiles = (num_tokens * heads) // LATENT_TC_TILE + num_seqs
+    tiles = (num_tokens * heads) // (16 if small_tiles else LATENT_TC_TILE) + num_seqs
     span = min(window, max_ctx) if window > 0 else max_ctx
     blocks = max(1, (span + LATENT_TC_TILE - 1) // LATENT_TC_TILE + 1)
     return max(1, min(blocks, 296 // tiles)) if tiles <= 148 else 1

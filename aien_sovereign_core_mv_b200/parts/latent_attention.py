@@ -88,7 +88,7 @@ class LatentAttention(Mixer):
             + n * self.kv_rank * lim.itemsize + n * self.value_dim * lim.itemsize + self.hidden_size * 4
         # the partial results of a step with few tiles: at most 296 CTAs' worth of 64 rows each
         split = 296 * K.LATENT_TC_TILE * (self.kv_rank + 2) * 4 + (lim.max_seqs + 1) * n * 296 * (self.kv_rank + 2) * 4 // 64
-        return lim.max_tokens * per_token + 16384 + split
+        return lim.max_tokens * per_token + 16384 + split + K.PARTIALS_MAX_BYTES
 
     # ---- one step
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
@@ -114,13 +114,14 @@ class LatentAttention(Mixer):
             K.rotate_pairs_rows(q, self.q_head, self.head_dim, qf, self.row, self.kv_rank, n, self.rot_dim, rdims, cos, sin)
         mixed = ws.take((T, n * self.kv_rank), ctx.dtype)
         if tc:
-            ksplit = K.latent_attention_tc_ksplit(T, ctx.num_seqs, n, ctx.max_ctx_len, self.window)
+            small = K.latent_attention_tc_small_tiles(ctx.decode_only, self.kv_rank)
+            ksplit = K.latent_attention_tc_ksplit(T, ctx.num_seqs, n, ctx.max_ctx_len, self.window, small)
             scratch = ws.take((K.latent_attention_tc_scratch(T, n, self.kv_rank, ksplit),), torch.float32) if ksplit > 1 else None
             K.latent_attention_tc(qf, cache, group.block_table, group.max_blocks, ctx.q_start, ctx.positions, mixed, ctx.num_seqs, n,
-                                  self.kv_rank, self.rot_dim, group.page_size, self.window, self.scale, self.sinks, ksplit, scratch)
+                                  self.kv_rank, self.rot_dim, group.page_size, self.window, self.scale, self.sinks, ksplit, scratch, small)
         else:
             K.latent_attention(qf, cache, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, mixed, n, self.kv_rank,
                                self.rot_dim, group.page_size, self.window, self.scale, self.sinks)
         o = ws.take((T, n * self.value_dim), ctx.dtype)
         K.head_project(mixed, self.kv_rank, 0, self.w_uv, o, self.value_dim, 0)
-        return linear(ctx, o, self.w_o, out_dtype=torch.float32)
+        return linear(ctx, o, self.w_o, out_dtype=torch.float32, may_defer_sum=True)     # the branch norm adds partial products

@@ -84,8 +84,8 @@ class ActMLP(FeedForward):
         self.w_up, self.w_down = tensors["up"].contiguous(), tensors["down"].contiguous()
 
     def workspace_bytes(self, lim):
-        return lim.max_tokens * (self.intermediate_size * lim.itemsize + self.hidden_size * 4) + 4096
+        return lim.max_tokens * (self.intermediate_size * lim.itemsize + self.hidden_size * 4) + 4096 + K.PARTIALS_MAX_BYTES
 
     def forward(self, ctx: StepContext, h: torch.Tensor):
         a = linear(ctx, h, self.w_up, act=self.act)
-        return linear(ctx, a, self.w_down, out_dtype=torch.float32)
+        return linear(ctx, a, self.w_down, out_dtype=torch.float32, may_defer_sum=True)    # the branch norm adds partial products

@@ -50,7 +50,7 @@ class DecayLinearAttention(Mixer):
 
     def workspace_bytes(self, lim):
         chunks = K.decay_linear_attention_scratch(lim.max_tokens, lim.max_seqs, self.num_heads, self.head_dim, self.value_dim) * 4
-        return lim.max_tokens * ((2 * self.qk_dim + 2 * self.v_dim) * 4 + self.v_dim * (4 + lim.itemsize) + self.hidden_size * 4) + 8192 + chunks
+        return lim.max_tokens * ((2 * self.qk_dim + 2 * self.v_dim) * 4 + self.v_dim * (4 + lim.itemsize) + self.hidden_size * 4) + 8192 + chunks + K.PARTIALS_MAX_BYTES
 
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
         T = ctx.num_tokens
@@ -66,7 +66,7 @@ class DecayLinearAttention(Mixer):
                                  o, ctx.num_seqs, self.num_heads, self.head_dim, self.value_dim, scratch, single_tokens=ctx.decode_only)
         y = ctx.workspace.take((T, self.v_dim), ctx.dtype)
         K.gated_rmsnorm(o, proj[:, 2 * self.qk_dim + self.v_dim:], self.norm_w, self.norm_eps, y)
-        return linear(ctx, y, self.w_o, out_dtype=torch.float32)
+        return linear(ctx, y, self.w_o, out_dtype=torch.float32, may_defer_sum=True)     # the branch norm adds partial products
 
 
 @register_mixer("gated_recurrence")
@@ -100,7 +100,7 @@ class GatedRecurrence(Mixer):
         return CacheNeed("state", state_shape=(self.width,), state_dtype="float32")
 
     def workspace_bytes(self, lim):
-        return lim.max_tokens * (3 * self.width * 4 + self.width * lim.itemsize + self.hidden_size * 4) + 8192
+        return lim.max_tokens * (3 * self.width * 4 + self.width * lim.itemsize + self.hidden_size * 4) + 8192 + K.PARTIALS_MAX_BYTES
 
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
         T, W = ctx.num_tokens, self.width
@@ -110,4 +110,4 @@ class GatedRecurrence(Mixer):
         y = ctx.workspace.take((T, W), ctx.dtype)
         K.gated_recurrence(proj, 0, W, 2 * W, self.b_z, self.b_x, state, group.slot_map, ctx.q_start, ctx.positions, y, ctx.num_seqs, W,
                            segments=not ctx.decode_only)
-        return linear(ctx, y, self.w_o, out_dtype=torch.float32)
+        return linear(ctx, y, self.w_o, out_dtype=torch.float32, may_defer_sum=True)     # the branch norm adds partial products

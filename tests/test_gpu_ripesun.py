@@ -325,7 +325,8 @@ def test_one_product_per_head(dtype, heads, n, k):
     assert float(np.abs(got[:, :, n:]).max()) == 0.0 and float(out[:, 0].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("dtype,impl", [(torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "tc")])
+@pytest.mark.parametrize("dtype,impl", [(torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "tc"), (torch.bfloat16, "tc_split"),
+                                        (torch.bfloat16, "tc_small")])
 @pytest.mark.parametrize("window,page,heads,r,rd", [(21, 16, 5, 40, 8), (64, 16, 17, 128, 32), (0, 8, 1, 96, 16), (16, 16, 4, 64, 64),
                                                      (7, 32, 3, 520, 0), (100, 16, 6, 256, 16), (0, 16, 16, 512, 64)])
 def test_latent_attention_sees_its_window_and_the_sink(dtype, impl, window, page, heads, r, rd):
@@ -334,12 +335,14 @@ def test_latent_attention_sees_its_window_and_the_sink(dtype, impl, window, page
     (distance window - 1), just outside (distance window) and at position 0 are scaled so that each would take nearly all
     the weight if it were seen; one head's sink is made large.  ``impl``: the plain kernel, or the tensor-core one."""
     from aien_sovereign_core_mv_b200 import kernels as K
-    if impl == "tc" and not K.latent_attention_tc_supports(dtype, r, rd):
+    if impl.startswith("tc") and not K.latent_attention_tc_supports(dtype, r, rd):
         pytest.skip("the tensor-core kernel does not take this size")
     g = torch.Generator().manual_seed(window + r)
     n, D, scale = 150, r + rd, 0.2
     rows = torch.randn(n, D, generator=g) * 0.5
     portions = [(0, 3), (page - 2, 4), (2 * page, 1), (60, 70), (149, 1)]
+    if impl == "tc_small":                                            # the tiles of 16 rows are for requests that bring one token each
+        portions = [(p, 1) for p in (0, 1, page - 1, page, 2 * page, 99, 100, 149)]
     qpos = [p0 + i for p0, m in portions for i in range(m)]
     loud = {p - far for p in qpos for far in ([window - 1, window] if window else [p]) if p - far >= 0}
     for j in sorted(loud):
@@ -351,7 +354,7 @@ def test_latent_attention_sees_its_window_and_the_sink(dtype, impl, window, page
         cache[order[j // page] * page + j % page] = rows[j]
     bt = torch.full((len(portions), 64), -1, dtype=torch.int32)
     bt[:, :(n + page - 1) // page] = torch.tensor(order[:(n + page - 1) // page], dtype=torch.int32)
-    qdt = torch.bfloat16 if impl == "tc" else torch.float32
+    qdt = torch.bfloat16 if impl.startswith("tc") else torch.float32
     q = (torch.randn(len(qpos), heads * D, generator=g) * 0.7).to(qdt)
     sinks = torch.randn(heads, generator=g)
     sinks[0] = 6.0
@@ -360,9 +363,11 @@ def test_latent_attention_sees_its_window_and_the_sink(dtype, impl, window, page
     starts = [0]
     for _, m in portions:
         starts.append(starts[-1] + m)
-    if impl == "tc":
+    if impl.startswith("tc"):
+        ksplit = {"tc": 1, "tc_split": 3, "tc_small": 2}[impl]
+        scratch = torch.full((K.latent_attention_tc_scratch(len(qpos), heads, r, ksplit),), float("nan")).cuda() if ksplit > 1 else None
         K.latent_attention_tc(q.cuda(), cache.cuda(), bt.cuda(), 64, i32(starts), i32(qpos), out, len(portions), heads, r, rd, page, window,
-                              scale, sinks.cuda())
+                              scale, sinks.cuda(), ksplit, scratch, small_tiles=(impl == "tc_small"))
     else:
         K.latent_attention(q.cuda(), cache.cuda(), bt.cuda(), 64, i32(seq_of), i32(qpos), out, heads, r, rd, page, window, scale, sinks.cuda())
     rn, qn = rows.double().numpy(), q.double().numpy().reshape(len(qpos), heads, D)
