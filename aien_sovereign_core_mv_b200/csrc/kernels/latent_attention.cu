@@ -183,7 +183,7 @@ latent_attention_kernel(const float* __restrict__ q, long ldq, const TKV* __rest
         for (int u = 0; u < CPL; ++u) acc[i][u] = 0.f;
     }
     for (int base = start; base <= pos; base += LT_KEYS) {
-        __syncthreads();                     // the tile before is used up (and Qs is written, first time round)
+        __syncthreads();                     // the tile before is used up (and Qs is written, the first time)
         if (tid < LT_KEYS) {
             const int j = base + tid;
             int slot = -1;

@@ -3,7 +3,7 @@
 // of the cache ([slots, ...]); everything that enters a recurrence (decay powers, gates,
 // candidates, the state itself, the products with it) is float32 in both engine precisions.
 //
-// The contract of a state slot, all of it on the device: the portion of request s of the step is
+// The rules of a state slot, all of them on the device: the portion of request s of the step is
 // the tokens q_start[s] .. q_start[s+1]; its slot is slot_map[s]; a portion whose first token has
 // position 0 starts from a zero state whatever the slot held.  A launch depends on the number of
 // requests and on the sizes only, so a step can be captured or recorded.

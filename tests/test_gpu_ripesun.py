@@ -60,9 +60,18 @@ CONFIGS = {
               {"type": "lightning", "mixer": _light(4, 64, 64, [0.8, 0.95, 0.99, 0.999]), "mlp": _dense(256)},
               {"type": "mingru", "mixer": {"width": 256}, "mlp": _dense(128)},
               {"type": "latent_attention", "mixer": _latent(4, 32, 64, 32, 64, 128, 16, 0.12, 777.0), "mlp": _dense(128)}]},
+    # no attention at all (no paged cache group), sizes no vector or tensor-core kernel takes: width 90, heads of 10 / 6, 50 channels
+    "D": {"architecture": "Ripesun", "vocab": 101, "width": 90, "norm": {"eps": 1e-5}, "residual_mult": 0.9, "token_side": {"dim": 9}, "layers": [
+        {"type": "mingru", "mixer": {"width": 50}, "mlp": _dense(30)},
+        {"type": "lightning", "mixer": _light(3, 10, 6, [0.25, 0.75, 0.995]), "mlp": None},
+        {"type": "mingru", "mixer": {"width": 34}, "mlp": _dense(22)}]},
+    # attention only (no state group), odd sizes: 3 heads of 10 + 6 rotated, latent of 18, windows of 5 and 33 on caches of their own
+    "E": {"architecture": "Ripesun", "vocab": 130, "width": 70, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5}, "logit_softcap": 5.0, "layers": [
+        {"type": "latent_attention", "mixer": _latent(3, 10, 6, 14, 18, 14, 5, 0.4, 77.0), "mlp": _dense(50)},
+        {"type": "latent_attention", "mixer": _latent(2, 6, 2, 6, 18, 22, 33, 0.5, 1e5), "mlp": None}]},
 }
-PAGE = {"A": 16, "B": 8, "C": 16}
-LENGTHS = {"A": [1, 9, 50, 131], "B": [2, 20, 77], "C": [5, 70, 150]}
+PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 8}
+LENGTHS = {"A": [1, 9, 50, 131], "B": [2, 20, 77], "C": [5, 70, 150], "D": [3, 40, 90], "E": [2, 41, 95]}
 FP32_TOL, BF16_TOL = 1e-4, 4e-2
 DTYPES = [("float32", FP32_TOL), ("bfloat16", BF16_TOL)]
 
@@ -428,7 +437,7 @@ def test_prefill_then_token_by_token(models, which, dtype, tol):
     steps = [([(rid, toks[:cut], [0, cut - 1])], [])] + [([(rid, [toks[i]], [0])], []) for i in range(cut, len(toks))]
     check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} decode")
     state = eng.cache_state()
-    assert state["check"] == "" and (which == "B" or state["metrics"]["window_releases"] > 0)
+    assert state["check"] == "" and (which in ("B", "D") or state["metrics"]["window_releases"] > 0)     # B keeps every key, D has none
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
