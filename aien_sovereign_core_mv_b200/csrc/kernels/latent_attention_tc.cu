@@ -3,19 +3,19 @@
 //
 // A cached row [c | k_rot] serves every head as key and (its first R numbers) as value, so the rows of the score
 // product are (token, head) pairs: the queries of a request's portion, laid out [token][head][R + rot], are one
-// matrix of len * heads rows.  One CTA of eight warps owns 64 such rows; a step has at most T * heads / 64 + S tiles,
-// and a CTA finds its request and offset from q_start.  Keys are visited in blocks of 64 aligned to absolute
-// positions, read through the block table into shared memory with cp.async (absent or unneeded rows zero-filled).
-// Warp w works on the 16 rows (w & 3) * 16...; for the scores it takes the keys of half (w >> 2) of the block, for the
-// weighted sum the channels of half (w >> 2) of the latent, so the two warps of a slab exchange their row maxima and
-// their probabilities (bfloat16) through shared memory.  Products run on mma.sync.m16n8k16 (bfloat16 in, float32
+// matrix of len * heads rows.  One CTA owns 64 such rows (16 for steps of single tokens); a step has at most
+// T * heads / 64 + S tiles, and a CTA finds its request and offset from q_start.  Keys are visited in blocks of 64 aligned
+// to absolute positions, read through the block table into shared memory with cp.async (absent or unneeded rows
+// zero-filled).  The warps of a 16-row slab deal out the block's keys for the scores and the latent's channels for the
+// weighted sum, so they exchange their row maxima and their probabilities (bfloat16) through shared memory.  Products run
+// on mma.sync.m16n8k16 (bfloat16 in, float32
 // accumulate) with ldmatrix-fed fragments; masks, the online softmax and the sink are float32 per row.
 #include "common.cuh"
 #include <math.h>
 
 namespace aien {
 
-constexpr int LX_BM = 64, LX_BN = 64, LX_THREADS = 256, LX_PSTR = LX_BN + 8;
+constexpr int LX_BM = 64, LX_BN = 64, LX_PSTR = LX_BN + 8;
 
 __device__ __forceinline__ void lx_cp_async16(uint32_t dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;
@@ -43,16 +43,17 @@ __device__ __forceinline__ uint32_t lx_pack(float lo, float hi) {
 }
 
 // SLABS: 16-row slabs of a tile (4: tiles of 64 rows, for portions; 1: tiles of 16 rows, for steps of single tokens, where
-// a request has only its heads as rows).  The 8 / SLABS warps of a slab deal out the keys of a block for the scores and
-// the channels for the weighted sum.
-template <int R, int SLABS>
-__global__ void __launch_bounds__(LX_THREADS, SLABS == 1 ? 2 : 1)
+// a request has only its heads as rows).  The WARPS / SLABS warps of a slab deal out the keys of a block for the scores and
+// the channels for the weighted sum (tiles of 64 rows run 16 warps: four to a slab, so that a warp's share of the weighted
+// sum, 16 rows x a quarter of the latent, leaves registers for loads in flight).
+template <int R, int SLABS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, SLABS == 1 ? 2 : 1)
 latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                            const int* __restrict__ positions, int S, __nv_bfloat16* __restrict__ out,
                            int H, int rd, int page_size, int window, float scale_log2e, const float* __restrict__ sinks,
                            int ksplit, float* __restrict__ part_o, float* __restrict__ part_ml) {
-    constexpr int BM = SLABS * 16, PARTS = 8 / SLABS, KP = LX_BN / PARTS, NJ = KP / 8, CHP = R / PARTS;
+    constexpr int BM = SLABS * 16, PARTS = WARPS / SLABS, KP = LX_BN / PARTS, NJ = KP / 8, CHP = R / PARTS, THREADS = WARPS * 32;
     constexpr int DT = CHP / 8;                  // n8 tiles of this warp's share of the channels
     static_assert(DT >= 2 && DT % 2 == 0, "a warp's share of the latent must be whole pairs of n8 tiles");
     const int D = R + rd, STR = D + 8, CH = D / 8, KS = D / 16;
@@ -89,7 +90,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     const int g = lane >> 2, c = lane & 3;
 
     const __nv_bfloat16* qbase = q + ((size_t)qs * H + row0) * D;
-    for (int idx = tid; idx < BM * CH; idx += LX_THREADS) {
+    for (int idx = tid; idx < BM * CH; idx += THREADS) {
         const int r = idx / CH, ch = idx - r * CH;
         const bool valid = r < nrows;
         lx_cp_async16(Qs_u + (uint32_t)(r * STR + ch * 8) * 2, qbase + (size_t)(valid ? r : 0) * D + ch * 8, valid);
@@ -114,7 +115,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         __syncthreads();
     }
     for (int kb = kb_begin + (int)blockIdx.y; kb <= kb_end; kb += ksplit) {
-        for (int idx = tid; idx < LX_BN * CH; idx += LX_THREADS) {
+        for (int idx = tid; idx < LX_BN * CH; idx += THREADS) {
             const int r = idx / CH, ch = idx - r * CH;
             const int key = kb * LX_BN + r;
             bool valid = key >= first && key <= pos_hi;
@@ -312,18 +313,18 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
     }
 }
 
-template <int R, int SLABS>
+template <int R, int SLABS, int WARPS>
 static int launch_latent_tc(const void* q, const void* cache, const int* bt, int max_blocks, const int* q_start, const int* positions,
                             int T, int S, void* out, int H, int rd, int page_size, int window, float scale, const float* sinks,
                             int ksplit, float* part_o, float* part_ml, cudaStream_t stream) {
     const int D = R + rd;
     constexpr int BM = SLABS * 16;
-    const size_t smem = (size_t)(BM + LX_BN) * (D + 8) * 2 + (size_t)BM * LX_PSTR * 2 + 8 * 16 * sizeof(float);
+    const size_t smem = (size_t)(BM + LX_BN) * (D + 8) * 2 + (size_t)BM * LX_PSTR * 2 + (size_t)WARPS * 16 * sizeof(float);
     if (smem > 227 * 1024) return AIEN_E_SHAPE;
-    auto kern = latent_attention_tc_kernel<R, SLABS>;
+    auto kern = latent_attention_tc_kernel<R, SLABS, WARPS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return AIEN_E_STATE;
     const long tiles = ((long)T * H) / BM + S;
-    kern<<<dim3((unsigned)tiles, ksplit), LX_THREADS, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, max_blocks, q_start,
+    kern<<<dim3((unsigned)tiles, ksplit), WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, max_blocks, q_start,
                                                                      positions, S, (__nv_bfloat16*)out, H, rd, page_size, window,
                                                                      scale * 1.4426950408889634f, sinks, ksplit, part_o, part_ml);
     if (ksplit > 1)
@@ -404,7 +405,7 @@ using namespace aien;
 
 AIEN_API int aien_latent_attention_tc_supports(int kv_rank, int rot_dim) {
     if (!(kv_rank == 64 || kv_rank == 128 || kv_rank == 256 || kv_rank == 512) || rot_dim < 0 || (rot_dim & 15)) return 0;
-    const size_t smem = (size_t)(LX_BM + LX_BN) * (kv_rank + rot_dim + 8) * 2 + (size_t)LX_BM * LX_PSTR * 2 + 2 * LX_BM * sizeof(float);
+    const size_t smem = (size_t)(LX_BM + LX_BN) * (kv_rank + rot_dim + 8) * 2 + (size_t)LX_BM * LX_PSTR * 2 + 16 * 16 * sizeof(float);
     return smem <= 227 * 1024 ? 1 : 0;
 }
 
@@ -423,7 +424,7 @@ AIEN_API int aien_latent_attention_tc(const void* q, const void* cache, const in
     if (ksplit < 1 || ksplit > 65535 || (ksplit > 1 && (part_o == nullptr || part_ml == nullptr || ((uintptr_t)part_o & 7)))) return AIEN_E_SHAPE;
 #define LX_CASE(RV, SL)                                                                                                          \
     if (kv_rank == RV)                                                                                                           \
-        return launch_latent_tc<RV, SL>(q, cache, block_table, max_blocks, q_start, positions, T, S, out, H, rot_dim, page_size,  \
+        return launch_latent_tc<RV, SL, (SL == 4 ? 16 : 8)>(q, cache, block_table, max_blocks, q_start, positions, T, S, out, H, rot_dim, page_size,  \
                                         window, scale, sinks, ksplit, part_o, part_ml, stream);
     if (small_tiles && kv_rank >= 128) {                   // tiles of 16 rows: a latent of 64 would leave a warp half a pair of n8 tiles
         LX_CASE(128, 1) LX_CASE(256, 1) LX_CASE(512, 1)
