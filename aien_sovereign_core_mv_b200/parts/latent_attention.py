@@ -86,8 +86,9 @@ class LatentAttention(Mixer):
         n = self.num_heads
         per_token = (self.q_rank + self.row) * 4 + self.q_rank * lim.itemsize + n * self.q_head * 4 + n * self.row * 4 \
             + n * self.kv_rank * lim.itemsize + n * self.value_dim * lim.itemsize + self.hidden_size * 4
-        # the partial results of a step with few tiles: at most 296 CTAs' worth of 64 rows each
-        split = 296 * K.LATENT_TC_TILE * (self.kv_rank + 2) * 4 + (lim.max_seqs + 1) * n * 296 * (self.kv_rank + 2) * 4 // 64
+        # the partial results of a step with few tiles: tokens * heads * ksplit rows, which latent_attention_tc_ksplit keeps
+        # below 296 tiles' worth of 64 rows
+        split = 296 * K.LATENT_TC_TILE * (self.kv_rank + 2) * 4
         return lim.max_tokens * per_token + 16384 + split + K.PARTIALS_MAX_BYTES
 
     # ---- one step
