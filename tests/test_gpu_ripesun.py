@@ -562,6 +562,8 @@ def test_greedy_generation_through_the_entry_point(models):
 
 
 def test_sampling_and_the_command_line(models):
+    """Sampling through the scheduler (temperature, top-p, top-k) runs and repeats under the same seed; the command line
+    generates the plain implementation's greedy tokens and describes the model."""
     import subprocess
     from aien_sovereign_core_mv_b200.engine.generate import Generator
     from aien_sovereign_core_mv_b200.sampling import SamplingParams
@@ -571,7 +573,16 @@ def test_sampling_and_the_command_line(models):
     a = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
     b = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
     assert [r.tokens for r in a] == [r.tokens for r in b] and all(len(r.tokens) == 12 for r in a)
+    cfg, tensors = load_plain(d)
+    seq, want = list(reqs[1]), []
+    for _ in range(5):
+        t = int(np.argmax(pr.forward(cfg, tensors, seq)[-1]))
+        seq.append(t); want.append(t)
     exe = os.path.join(H.ROOT, "bin", "aien-b200")
+    out = subprocess.run([exe, "generate", "--model-dir", d, "--dtype", "float32", "--prompt-ids", ",".join(map(str, reqs[1])),
+                          "--max-tokens", "5", "--temperature", "0", "--stop-token-ids", "", "--json"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert json.loads(out.stdout.strip().splitlines()[-1])["tokens"] == [want]
     info = subprocess.run([exe, "info", "--model-dir", d], capture_output=True, text=True, timeout=600)
     assert info.returncode == 0, info.stderr[-2000:]
     rec = json.loads(info.stdout.strip().splitlines()[-1])
