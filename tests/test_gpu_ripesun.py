@@ -599,3 +599,88 @@ def test_trace_replay_from_the_command(models, tmp_path):
     assert sorted(out) == [0, 2]
     H.assert_close(out[0], np.stack([want[3][0], want[3][39], want[1][0]]), FP32_TOL, "trace step 0")
     H.assert_close(out[2], want[3][-1:], FP32_TOL, "trace step 2")
+
+
+# ------------------------------------------------------------------ configurations drawn at random
+def _random_config(rng):
+    """Sizes, order of layers, windows, sharing of caches, decays and constants drawn at random."""
+    width = rng.choice([64, 72, 96, 128, 160])
+    layers, own = [], []
+    for i in range(rng.randint(3, 7)):
+        kind = rng.choice(["latent_attention", "lightning", "mingru"])
+        mlp = None if rng.random() < 0.2 else _dense(rng.choice([24, 40, 64, 96]))
+        if kind == "latent_attention":
+            j = rng.choice(own) if own and rng.random() < 0.4 else None
+            if j is not None:
+                kv_rank, rot_dim, base = layers[j]["mixer"]["kv_rank"], layers[j]["mixer"]["rot_dim"], layers[j]["mixer"]["rot"]["base"]
+            else:
+                kv_rank, rot_dim, base = rng.choice([16, 24, 40, 64, 128]), rng.choice([8, 16, 32, 6]), rng.choice([1e4, 1e6, 500.0])
+            window = rng.choice([0, 5, 16, 33, 40, 100])
+            if j is not None and (((layers[j]["mixer"].get("mask") or {}).get("size") or 0) == 0) != (window == 0):
+                window = (layers[j]["mixer"].get("mask") or {}).get("size") or 0          # a cache that keeps all has readers that see all
+            dim = rng.choice([8, 16, 24, 32, 64])
+            layers.append({"type": kind, "mlp": mlp, "mixer": _latent(rng.choice([1, 2, 3, 4, 6, 17]), dim, rot_dim, rng.choice([8, 16, dim, 40]),
+                                                                     kv_rank, rng.choice([16, 24, 48, 96]), window, (dim + rot_dim) ** -0.5, base, j)})
+            if j is None:
+                own.append(i)
+        elif kind == "lightning":
+            heads = rng.choice([1, 2, 4, 5])
+            layers.append({"type": kind, "mlp": mlp, "mixer": _light(heads, rng.choice([8, 16, 64, 20]), rng.choice([8, 32, 12, 72]),
+                                                                    [rng.choice([0.5, 0.9, 0.97, 0.999, 1.0]) for _ in range(heads)])})
+        else:
+            layers.append({"type": kind, "mlp": mlp, "mixer": {"width": rng.choice([32, 50, 128])}})
+    cfg = {"architecture": "Ripesun", "vocab": rng.choice([101, 256, 333]), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])},
+           "embedding": {"scale": rng.choice([1.0, 4.0, 12.0])}, "residual_mult": rng.choice([0.5, 0.7, 1.0]),
+           "logit_softcap": rng.choice([15.0, 30.0]), "layers": layers}
+    side = rng.choice([0, 4, 8, 24])
+    if side:
+        cfg["token_side"] = {"dim": side}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Whole prompts, portions of changing size and three requests side by side, against the plain implementation.  float32
+    must agree to rounding.  bfloat16 is held to a loose bound only: in a model this small one token whose branch output lies
+    near zero before a norm can move a logit by a tenth through rounding alone, while a wrong key, mask or state moves it by
+    its whole size."""
+    import random
+    from aien_sovereign_core_mv_b200 import write_random_model
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    d = write_random_model(os.path.join(str(tmp_path), "m"), cfg, 1000 + seed)
+    c, tensors = load_plain(d)
+    draw = np.random.default_rng(seed)
+    reqs = {i + 1: [int(x) for x in draw.integers(0, cfg["vocab"], n)] for i, n in enumerate([rng.randint(1, 30), rng.randint(60, 120), rng.randint(100, 150)])}
+    want = {r: pr.forward(c, tensors, t) for r, t in reqs.items()}
+
+    def steps(mode):
+        if mode == "whole":
+            return [([(rid, t, list(range(len(t))))], [rid]) for rid, t in reqs.items()]
+        out = []
+        if mode == "portions":
+            for rid, t in reqs.items():
+                at = 0
+                while at < len(t):
+                    n = min(rng.choice([1, 2, 3, 7, 16, 33, 64]), len(t) - at)
+                    out.append(([(rid, t[at:at + n], list(range(n)))], [rid] if at + n == len(t) else []))
+                    at += n
+            return out
+        at, live = {r: 0 for r in reqs}, list(reqs)
+        while live:
+            entries, end = [], []
+            for rid in list(live):
+                n = min(len(reqs[rid]) - at[rid], 1 if rng.random() < 0.5 else rng.randint(2, 50))
+                entries.append((rid, reqs[rid][at[rid]:at[rid] + n], list(range(n))))
+                at[rid] += n
+                if at[rid] == len(reqs[rid]):
+                    end.append(rid); live.remove(rid)
+            out.append((entries, end))
+        return out
+
+    for dtype, tol in (("float32", FP32_TOL), ("bfloat16", 0.25)):
+        for mode in ("whole", "portions", "side by side"):
+            eng = H.engine_for(d, dtype, rng.choice([8, 16, 32]), 512, max_requests=4)
+            check(H.run_steps(eng, steps(mode)), want, tol, f"seed {seed} {dtype} {mode}")
+            assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
